@@ -83,3 +83,38 @@ TS_EXPORT int ts_gelu_gate_rows(void* x, const void* table, int act_dtype, const
                      ld, col0, V, total);
   return TS_ERR_BAD_ARGUMENT;
 }
+
+// weighted_sum: out[i] = sum_j scale[j] * in_j[i] over up to four inputs of the activation type,
+// summed in float32 and rounded once (branches of a layer that run side by side).
+struct WeightedInputs {
+  const void* in[4];
+  float scale[4];
+  int count;
+};
+
+template <typename TA>
+__global__ void weighted_sum_kernel(WeightedInputs w, TA* __restrict__ out, size_t n) {
+  ts_pdl_prologue();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+      if (j < w.count) acc = fmaf(w.scale[j], ts_to_float(static_cast<const TA*>(w.in[j])[i]), acc);
+    out[i] = ts_from_float<TA>(acc);
+  }
+}
+
+TS_EXPORT int ts_weighted_sum(const void* a, const void* b, const void* c, const void* d, float sa, float sb, float sc, float sd, int count,
+                              void* out, int act_dtype, long long n, void* stream) {
+  if (n <= 0) return 0;
+  if (count < 1 || count > 4) return TS_ERR_BAD_ARGUMENT;
+  WeightedInputs w = {{a, b, c, d}, {sa, sb, sc, sd}, count};
+  for (int j = 0; j < count; ++j)
+    if (w.in[j] == nullptr) return TS_ERR_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)min((n + 255) / 256, (long long)148 * 16);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (act_dtype == TS_DTYPE_F32) return ts_launch(weighted_sum_kernel<float>, dim3(blocks), dim3(256), 0, s, w, (float*)out, (size_t)n);
+  if (act_dtype == TS_DTYPE_BF16)
+    return ts_launch(weighted_sum_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, w, (__nv_bfloat16*)out, (size_t)n);
+  return TS_ERR_BAD_ARGUMENT;
+}

@@ -7,7 +7,9 @@
 // queries see only their own block of `chunk` positions (blocks count from position 0 of the
 // sequence; the larger bound holds where a layer has both); s = (q . k) * scale; softmax over
 // the keys; o = sum p * v.  With `has_sink` the softmax's denominator also holds exp(sink_score):
-// a key that every query sees, whose score is fixed and which has no value.  Scores, running
+// a key that every query sees, whose score is fixed and which has no value; with `head_sinks` that
+// score is a number per query head, read from device memory.  With `softcap` > 0 the scaled score
+// passes through softcap * tanh(s / softcap) before the softmax.  Scores, running
 // max and sum, and the output accumulate in float32
 // (engine/nn/sdpa.py:56,85-102 of the reference: scale head_dim^-0.5, causal, GQA by head
 // ratio, keys and values read through the block table).  Key j of sequence b lives at
@@ -27,7 +29,7 @@ __global__ void attention_paged_simple_kernel(
     const TA* __restrict__ q, const TA* __restrict__ kcache, const TA* __restrict__ vcache,
     TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_index,
     const int* __restrict__ block_table, int max_blocks, int page, int T, int nq, int nkv, int d,
-    float scale, int window, int chunk, int has_sink, float sink_score) {
+    float scale, int window, int chunk, int has_sink, float sink_score, float softcap, const float* __restrict__ head_sinks) {
   ts_pdl_prologue();
   __shared__ float qs[ATS_WARPS][ATS_MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -66,7 +68,7 @@ __global__ void attention_paged_simple_kernel(
       const TA* krow = kcache + (slot * nkv + hk) * d;
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot += qs[warp][i] * ts_to_float(krow[i]);
-      s = dot;
+      s = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
     }
     const float m_new = fmaxf(m, ts_warp_max(s));
     const float corr = expf(m - m_new);  // m = -inf on the first round: exp(-inf) = 0
@@ -87,7 +89,8 @@ __global__ void attention_paged_simple_kernel(
     }
     m = m_new;
   }
-  if (has_sink) {  // the sink joins the denominator only: the sums of values shrink with it
+  if (head_sinks != nullptr) sink_score = head_sinks[g];
+  if (has_sink || head_sinks != nullptr) {  // the sink joins the denominator only: the sums of values shrink with it
     const float m_new = fmaxf(m, sink_score);
     const float corr = expf(m - m_new);
     l = l * corr + expf(sink_score - m_new);
@@ -108,7 +111,7 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
                                         const int* seq_index, const int* block_table,
                                         int max_blocks, int page, int T, int nq, int nkv, int d,
                                         float scale, int window, int chunk, int has_sink, float sink_score,
-                                        void* stream) {
+                                        float softcap, const float* head_sinks, void* stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page <= 0 || max_blocks <= 0)
     return TS_ERR_BAD_ARGUMENT;
@@ -119,12 +122,12 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(attention_paged_simple_kernel<float>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const float*)q, (const float*)kcache, (const float*)vcache, (float*)out, positions,
-        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window, chunk, has_sink, sink_score);
+        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window, chunk, has_sink, sink_score, softcap, head_sinks);
   else if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(attention_paged_simple_kernel<__nv_bfloat16>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
         (__nv_bfloat16*)out, positions, seq_index, block_table, max_blocks, page, T, nq, nkv, d,
-        scale, window, chunk, has_sink, sink_score);
+        scale, window, chunk, has_sink, sink_score, softcap, head_sinks);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

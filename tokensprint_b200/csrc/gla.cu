@@ -63,7 +63,8 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const float* __restrict__ decay,
     float q_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
     float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, int tb, int segs, int seg_len, float* __restrict__ seg_state,
-    float* __restrict__ seg_decay, float* __restrict__ seg_start) {
+    float* __restrict__ seg_decay, float* __restrict__ seg_start, const float* __restrict__ kscale, int decay_scalar, int groups, int ev,
+    long long slot_stride) {
   ts_pdl_prologue();
   extern __shared__ __align__(16) float sm[];
   // staged per token: q, k, decay [dp] each, v [cols]
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   const int col = col0 + cj;
   const bool has_col = col < e;
   const int c0 = r * KP;
-  float* S = state + (((size_t)state_slots[b] * H + h) * d) * e;
+  float* S = state + (size_t)state_slots[b] * slot_stride + ((size_t)h * d) * e;
   const size_t state_elems = (size_t)d * e;
   float* seg_L = MODE == 0 ? nullptr : seg_state + (((size_t)b * segs + seg) * H + h) * state_elems;   // this segment's end state
   float* seg_P = MODE == 0 ? nullptr : seg_decay + (((size_t)b * segs + seg) * H + h) * d;             // this segment's decay product
@@ -122,10 +123,10 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     for (int i = 0; i < KP; ++i) p_reg[i] = 1.f;
   }
 
-  const size_t qk_off = (size_t)h * d, v_off = (size_t)h * e + col0;
+  const size_t qk_off = (size_t)(h / (H / groups)) * d, a_off = (size_t)h * d, v_off = (size_t)h * ev + col0;
   // what this thread fetches for a round: entries threadIdx.x + j * GLA_THREADS of the round's [tokens][dp] and [tokens][cols]
   TA fq[GLA_PF], fk[GLA_PF], fv[GLA_PFV];
-  float fa[GLA_PF];
+  float fa[GLA_PF], fb[GLA_PF];
   // Entry i of a round is channel i % dp of token i / dp (for v: column i % cols of token i / cols); a thread's
   // entries lie GLA_THREADS apart, so their places are found once, by steps, without a division per entry.
   const int Hd = H * d;
@@ -142,7 +143,8 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
         const size_t at = (size_t)tr * ld_qkv + qk_off + cr;
         fq[j] = gla_load(q + at);
         fk[j] = gla_load(k + at);
-        fa[j] = gla_load(decay + (size_t)tr * Hd + qk_off + cr);
+        fa[j] = decay_scalar ? gla_load(decay + (size_t)tr * H + h) : gla_load(decay + (size_t)tr * Hd + a_off + cr);
+        fb[j] = kscale ? gla_load(kscale + (size_t)tr * H + h) : 1.f;
       }
       tt += step_t, c += step_c;
       if (c >= dp) c -= dp, ++tt;
@@ -150,7 +152,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     tt = vfirst_t, c = vfirst_c;
 #pragma unroll
     for (int j = 0; j < GLA_PFV; ++j) {
-      fv[j] = gla_load(v + (size_t)(t0 + min(tt, nt - 1)) * ld_qkv + v_off + min(c, e - 1 - col0));
+      fv[j] = gla_load(v + (size_t)(t0 + min(tt, nt - 1)) * ld_qkv + v_off + min(c, ev - 1 - col0));
       tt += vstep_t, c += vstep_c;
       if (c >= cols_per_cta) c -= cols_per_cta, ++tt;
     }
@@ -164,7 +166,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
         const bool real = c < d;
         const int i = tt * dp + c;
         sq[i] = real ? ts_to_float(fq[j]) * q_scale : 0.f;
-        sk[i] = real ? ts_to_float(fk[j]) : 0.f;
+        sk[i] = real ? ts_to_float(fk[j]) * fb[j] : 0.f;
         sa[i] = real ? fa[j] : 1.f;
       }
       tt += step_t, c += step_c;
@@ -173,7 +175,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     tt = vfirst_t, c = vfirst_c;
 #pragma unroll
     for (int j = 0; j < GLA_PFV; ++j) {
-      if (tt < nt) sv[tt * cols_per_cta + c] = (col0 + c < e) ? ts_to_float(fv[j]) : 0.f;
+      if (tt < nt) sv[tt * cols_per_cta + c] = (col0 + c < ev) ? ts_to_float(fv[j]) : (col0 + c < e ? 1.f : 0.f);
       tt += vstep_t, c += vstep_c;
       if (c >= cols_per_cta) c -= cols_per_cta, ++tt;
     }
@@ -239,10 +241,19 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   }
 }
 
+// What the general form of the recurrence has beyond gated linear attention's (see ts_linear_scan).
+struct GlaExtra {
+  const float* kscale;    // [T, H] a factor on k per (token, head), or null
+  int decay_scalar;       // 1: decay is [T, H], one number per (token, head) for all key channels
+  int groups;             // q and k have `groups` heads; head h reads group h / (H / groups)
+  int ev;                 // columns of v per head; the state has e >= ev columns, column ev (if any) sees the value 1
+  long long slot_stride;  // floats from one request's state to the next
+};
+
 template <typename TA, int KP, int MODE>
 static int launch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
                            const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, int segs, int seg_len,
-                           float* scratch, cudaStream_t s) {
+                           float* scratch, cudaStream_t s, const GlaExtra& x) {
   const int cols = GLA_THREADS / R, dp = R * KP;
   // tokens per round: what the threads' fetch registers hold, at most GLA_TB
   const int tb = min(GLA_TB, min(GLA_THREADS * GLA_PF / dp, GLA_THREADS * GLA_PFV / cols));
@@ -255,25 +266,26 @@ static int launch_gla_scan(const void* q, const void* k, const void* v, long lon
   float* seg_decay = scratch ? seg_state + (size_t)B * segs * H * d * e : nullptr;
   float* seg_start = scratch ? seg_decay + (size_t)B * segs * H * d : nullptr;
   return ts_launch(gla_scan_kernel<TA, KP, MODE>, grid, dim3(GLA_THREADS), smem, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, decay,
-                   q_scale, state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb, segs, seg_len, seg_state, seg_decay, seg_start);
+                   q_scale, state, state_slots, cu_seqlens, o, H, d, e, R, cols, tb, segs, seg_len, seg_state, seg_decay, seg_start, x.kscale,
+                   x.decay_scalar, x.groups, x.ev, x.slot_stride);
 }
 
 template <typename TA, int KP>
 static int launch_gla_scan_modes(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
                                  const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int R, int segs,
-                                 int seg_len, float* scratch, cudaStream_t s) {
+                                 int seg_len, float* scratch, cudaStream_t s, const GlaExtra& x) {
   if (segs <= 1)
-    return launch_gla_scan<TA, KP, 0>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, 1, 0, nullptr, s);
+    return launch_gla_scan<TA, KP, 0>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, 1, 0, nullptr, s, x);
   const int st = launch_gla_scan<TA, KP, 1>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len,
-                                            scratch, s);
+                                            scratch, s, x);
   if (st != 0) return st;
-  return launch_gla_scan<TA, KP, 2>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s);
+  return launch_gla_scan<TA, KP, 2>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s, x);
 }
 
 template <typename TA>
 static int dispatch_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, const float* decay, float q_scale, float* state,
                              const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int segs, int seg_len,
-                             float* scratch, cudaStream_t s) {
+                             float* scratch, cudaStream_t s, const GlaExtra& x) {
   // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
   int R = 1;
   while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
@@ -291,7 +303,7 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   static_assert(GLA_MAX_KP % 4 == 0, "a thread's channels come in fours");
 #define GLA_CASE(KP) \
   if (kp <= KP) \
-    return launch_gla_scan_modes<TA, KP>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s)
+    return launch_gla_scan_modes<TA, KP>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, R, segs, seg_len, scratch, s, x)
   GLA_CASE(4);
   GLA_CASE(8);
   GLA_CASE(12);
@@ -348,11 +360,39 @@ TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long
   if (H <= 0 || d <= 0 || e <= 0 || segs < 1 || (segs > 1 && (seg_len < 1 || scratch == nullptr))) return TS_ERR_BAD_ARGUMENT;
   if ((long long)B * segs > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
+  const GlaExtra x = {nullptr, 0, H, e, (long long)H * d * e};
   if (act_dtype == TS_DTYPE_F32)
-    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len, scratch, s);
+    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len, scratch, s, x);
   if (act_dtype == TS_DTYPE_BF16)
     return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len,
-                                            scratch, s);
+                                            scratch, s, x);
+  return TS_ERR_BAD_ARGUMENT;
+}
+
+// The same recurrence in its general form, for mixers whose decay is one number per (token, head):
+//   S_t = a_t S_(t-1) + (b_t k_t) v_t^T,   o_t = S_t^T (q_t * q_scale)
+// decay = a [T, H] float32 (`decay_scalar` = 1; 0: [T, H*d] as above); kscale = b [T, H] float32 or null;
+// q, k [T, groups*d] (head h reads group h / (H / groups)) and v [T, H*ev], views with the common row
+// stride ld_qkv; the state of a request starts `slot_stride` floats after the one before it and holds
+// [H, d, e] with e = ev or ev + 1: a column beyond v's sees the value 1 in every token, so that it
+// carries sum_t (products of decays) b_t k_t, the normaliser of a matrix memory, and its read-out
+// n_t . q_t arrives as column ev of o [T, H*e].
+TS_EXPORT int ts_linear_scan(const void* q, const void* k, const void* v, long long ld_qkv, int act_dtype, const float* decay,
+                             int decay_scalar, const float* kscale, float q_scale, float* state, long long slot_stride, const int* state_slots,
+                             const int* cu_seqlens, float* o, int B, int H, int groups, int d, int ev, int e, int segs, int seg_len,
+                             float* scratch, void* stream) {
+  if (B <= 0) return 0;
+  if (H <= 0 || d <= 0 || ev <= 0 || (e != ev && e != ev + 1) || groups <= 0 || H % groups || segs < 1 ||
+      (segs > 1 && (seg_len < 1 || scratch == nullptr)) || slot_stride < (long long)H * d * e)
+    return TS_ERR_BAD_ARGUMENT;
+  if ((long long)B * segs > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
+  cudaStream_t s = (cudaStream_t)stream;
+  const GlaExtra x = {kscale, decay_scalar ? 1 : 0, groups, ev, slot_stride};
+  if (act_dtype == TS_DTYPE_F32)
+    return dispatch_gla_scan<float>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len, scratch, s, x);
+  if (act_dtype == TS_DTYPE_BF16)
+    return dispatch_gla_scan<__nv_bfloat16>(q, k, v, ld_qkv, decay, q_scale, state, state_slots, cu_seqlens, o, B, H, d, e, segs, seg_len,
+                                            scratch, s, x);
   return TS_ERR_BAD_ARGUMENT;
 }
 

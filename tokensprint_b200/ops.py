@@ -35,7 +35,7 @@ _SIGNATURES = {
     ],
     "ts_attention_paged_simple": [
         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_float, _c_void_p,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_void_p,
     ],
     "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
@@ -404,15 +404,23 @@ def attention_paged_simple(
     window: int = 0,
     chunk: int = 0,
     sink: Optional[float] = None,
+    softcap: float = 0.0,
+    head_sinks: Optional[torch.Tensor] = None,
 ) -> None:
     """Causal attention over the paged cache on CUDA cores (float32 or bfloat16).
 
     q/out [T,nq*d]; caches [pages,page,nkv,d]; positions, seq_index [T] i32;
     block_table [B,max_blocks] i32.  window > 0: a query sees its last `window` keys.
     chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count
-    from position 0).  sink: a score that joins every softmax's denominator without a value.
+    from position 0).  sink: a score that joins every softmax's denominator without a value;
+    head_sinks [nq] float32: one such score per query head.  softcap > 0: the scaled score goes
+    through softcap * tanh(s / softcap).
     """
     flush_gemm_chain()
+    if head_sinks is not None:
+        _cuda_contig("head_sinks", head_sinks, torch.float32)
+        if head_sinks.numel() != num_heads:
+            raise KernelError(f"attention: head_sinks must have one entry per query head ({num_heads}), got {head_sinks.numel()}")
     _cuda_contig("q", q)
     _cuda_contig("k_cache", k_cache, q.dtype)
     _cuda_contig("v_cache", v_cache, q.dtype)
@@ -436,7 +444,7 @@ def attention_paged_simple(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _act_code("q", q), out.data_ptr(),
         positions.data_ptr(), seq_index.data_ptr(), block_table.data_ptr(), block_table.shape[1],
         page_size, T, nq, nkv, d, float(scale), int(window), int(chunk), 0 if sink is None else 1,
-        0.0 if sink is None else float(sink), _stream()))
+        0.0 if sink is None else float(sink), float(softcap), _ptr(head_sinks), _stream()))
 
 
 def sample(
@@ -735,6 +743,310 @@ def gla_norm_gate(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out
         raise KernelError("gla_norm_gate: shapes disagree")
     _check("gla_norm_gate", _fn("ts_gla_norm_gate")(o.data_ptr(), gate.data_ptr(), gate.stride(0), _act_code("out", out), weight.data_ptr(),
                                                     out.data_ptr(), T, H, e, float(eps), _stream()))
+
+
+
+# ---------------------------------------------------------------------------
+# the linear recurrence in its general form, and what stands around it in mixers whose decay is one
+# number per (token, head)
+
+_SIGNATURES.update({
+    "ts_linear_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_ll, _c_void_p,
+                       _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
+    "ts_rows_dot_f32": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_mlstm_gate_scan": [_c_void_p, _c_float, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "ts_mlstm_norm_gate": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
+    "ts_ssm_conv": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
+                    _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
+    "ts_ssm_conv_state": [_c_void_p, _c_int, _c_ll, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "ts_ssm_gate_norm": [_c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int,
+                         _c_float, _c_void_p],
+    "ts_scale_rows": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "ts_rope_table": [_c_void_p, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
+    "ts_qkv_prepare": [_c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float,
+                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_gate_rows": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_weighted_sum": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_float, _c_float, _c_float, _c_int, _c_void_p, _c_int, _c_ll,
+                        _c_void_p],
+})
+
+
+def _matrix_view(name: str, t: torch.Tensor, rows: int, cols: int, dtype: Optional[torch.dtype] = None) -> None:
+    if not t.is_cuda or t.dim() != 2 or t.stride(1) != 1 or tuple(t.shape) != (rows, cols) or (dtype is not None and t.dtype != dtype):
+        raise KernelError(f"{name} must be a CUDA matrix [{rows}, {cols}]{'' if dtype is None else ' of ' + str(dtype)} with unit inner stride, "
+                          f"got {tuple(t.shape)} {t.dtype}")
+
+
+def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, kscale: Optional[torch.Tensor], q_scale: float,
+                state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, num_seqs: int, num_heads: int,
+                groups: int, key_dim: int, value_dim: int, normaliser: bool = False, max_seqlen: Optional[int] = None) -> None:
+    """S_t = a_t S_(t-1) + (b_t k_t) v_t^T,  out_t = S_t^T (q_t * q_scale), per head, over the step's tokens
+    sequence by sequence, with one decay a_t per (token, head).
+
+    q, k [T, groups*d] (head h reads group h // (H // groups)) and v [T, H*e]: views with one common
+    row stride, float32 or bfloat16 (all three alike); decay [T, H] and kscale [T, H] (or None) float32.
+    state [slots, n] float32 with n >= H*d*e': a request's [H, d, e'] block stands at the start of its
+    row, e' = e + 1 with `normaliser` (the extra column is fed the value 1 in every token, so it holds
+    the sum of the decayed b_t k_t, and its read-out arrives as column e of out), else e' = e.
+    out [T, H*e'] float32.  Long portions run in segments side by side as in gla_scan."""
+    flush_gemm_chain()
+    H, G, d, e = int(num_heads), int(groups), int(key_dim), int(value_dim)
+    ee = e + 1 if normaliser else e
+    if d > GLA_MAX_KEY_DIM:
+        raise KernelError(f"linear_scan: at most {GLA_MAX_KEY_DIM} key channels per head, got {d}")
+    if G < 1 or H % G:
+        raise KernelError(f"linear_scan: {H} heads are no multiple of {G} groups")
+    T = q.shape[0]
+    _matrix_view("linear_scan: q", q, T, G * d)
+    _matrix_view("linear_scan: k", k, T, G * d, q.dtype)
+    _matrix_view("linear_scan: v", v, T, H * e, q.dtype)
+    if not (q.stride(0) == k.stride(0) == v.stride(0)):
+        raise KernelError("linear_scan: q, k and v must share one row stride")
+    _cuda_contig("decay", decay, torch.float32)
+    if kscale is not None:
+        _cuda_contig("kscale", kscale, torch.float32)
+    for name, t in (("decay", decay), ("kscale", kscale)):
+        if t is not None and tuple(t.shape) != (T, H):
+            raise KernelError(f"linear_scan: {name} must be [{T}, {H}], got {tuple(t.shape)}")
+    _cuda_contig("state_slots", state_slots, torch.int32)
+    _cuda_contig("cu_seqlens", cu_seqlens, torch.int32)
+    _cuda_contig("out", out, torch.float32)
+    if not state.is_cuda or state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * d * ee:
+        raise KernelError(f"linear_scan: state must be float32 [slots, >= {H * d * ee}], got {tuple(state.shape)} {state.dtype}")
+    if out.shape != (T, H * ee):
+        raise KernelError(f"linear_scan: out must be [{T}, {H * ee}], got {tuple(out.shape)}")
+    if state_slots.numel() < num_seqs or cu_seqlens.numel() < num_seqs + 1:
+        raise KernelError("linear_scan: state_slots and cu_seqlens are shorter than the batch")
+    segs, seg_len = gla_segments(int(num_seqs), max_seqlen)
+    scratch = None
+    if segs > 1:
+        need = int(num_seqs) * segs * H * d * ee + int(num_seqs) * segs * H * d + int(num_seqs) * H * d * ee
+        scratch = torch.empty(need, device=q.device, dtype=torch.float32)
+    _check("linear_scan", _fn("ts_linear_scan")(
+        q.data_ptr(), k.data_ptr(), v.data_ptr(), q.stride(0), _act_code("q", q), decay.data_ptr(), 1, _ptr(kscale), float(q_scale),
+        state.data_ptr(), state.stride(0), state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, G, d, e, ee,
+        segs, seg_len, _ptr(scratch), _stream()))
+    if segs > 1:
+        global launch_count
+        launch_count += 1  # the recurrence ran as two kernels
+
+
+def rows_dot_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], out: torch.Tensor) -> None:
+    """out[t, r] = x[t] . weight[r] + bias[r] with float32 weights and sums; x [T, W] float32 or
+    bfloat16 (any row stride), weight [R, W] float32, out [T, R] float32."""
+    flush_gemm_chain()
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("out", out, torch.float32)
+    T, (R, W) = x.shape[0], weight.shape
+    _matrix_view("rows_dot_f32: x", x, T, W)
+    if bias is not None:
+        _cuda_contig("bias", bias, torch.float32)
+    if out.shape != (T, R) or (bias is not None and bias.numel() != R):
+        raise KernelError("rows_dot_f32: shapes disagree")
+    _check("rows_dot_f32", _fn("ts_rows_dot_f32")(x.data_ptr(), _act_code("x", x), x.stride(0), weight.data_ptr(), _ptr(bias), out.data_ptr(),
+                                                  T, R, W, _stream()))
+
+
+def mlstm_gate_scan(pre: torch.Tensor, cap: float, m_state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, num_seqs: int,
+                    num_heads: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """From pre [T, 2H] float32 (input-gate rows, then forget-gate rows): the running maximum m of the
+    gates' logarithms per (token, head), carried in m_state [slots, >= H] (a view whose rows are the
+    requests' slots), and what the recurrence needs of it: decay = exp(log_f + m_prev - m) and
+    kscale = exp(log_i - m), each [T, H] float32.  Returns (decay, kscale, m)."""
+    H = int(num_heads)
+    _cuda_contig("pre", pre, torch.float32)
+    T = pre.shape[0]
+    if pre.shape != (T, 2 * H):
+        raise KernelError(f"mlstm_gate_scan: pre must be [{T}, {2 * H}], got {tuple(pre.shape)}")
+    if not m_state.is_cuda or m_state.dtype != torch.float32 or m_state.dim() != 2 or m_state.stride(1) != 1 or m_state.shape[1] < H:
+        raise KernelError("mlstm_gate_scan: m_state must be a float32 view [slots, >= heads]")
+    decay = torch.empty((T, H), device=pre.device, dtype=torch.float32)
+    kscale = torch.empty_like(decay)
+    m = torch.empty_like(decay)
+    _check("mlstm_gate_scan", _fn("ts_mlstm_gate_scan")(pre.data_ptr(), float(cap), m_state.data_ptr(), m_state.stride(0), state_slots.data_ptr(),
+                                                        cu_seqlens.data_ptr(), decay.data_ptr(), kscale.data_ptr(), m.data_ptr(),
+                                                        int(num_seqs), H, _stream()))
+    return decay, kscale, m
+
+
+def mlstm_norm_gate(o: torch.Tensor, m: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, num_heads: int,
+                    value_dim: int, eps: float) -> None:
+    """o [T, H*(e+1)] float32 from linear_scan with its normaliser column; m [T, H]; per head
+    h = o[:e] / (max(|o[e]|, exp(-m)) + 1e-6), then h / sqrt(mean(h^2) + eps) * weight[h*e:(h+1)*e] *
+    sigmoid(gate) into out [T, H*e] (the compute type, like gate)."""
+    H, e = int(num_heads), int(value_dim)
+    _cuda_contig("o", o, torch.float32)
+    _cuda_contig("m", m, torch.float32)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("out", out)
+    T = o.shape[0]
+    _matrix_view("mlstm_norm_gate: gate", gate, T, H * e, out.dtype)
+    if o.shape != (T, H * (e + 1)) or out.shape != (T, H * e) or weight.numel() != H * e or m.shape != (T, H):
+        raise KernelError("mlstm_norm_gate: shapes disagree")
+    _check("mlstm_norm_gate", _fn("ts_mlstm_norm_gate")(o.data_ptr(), m.data_ptr(), gate.data_ptr(), gate.stride(0), _act_code("out", out),
+                                                        weight.data_ptr(), out.data_ptr(), T, H, e, float(eps), _stream()))
+
+
+def ssm_conv(xin: torch.Tensor, taps: torch.Tensor, bias: torch.Tensor, conv_state: torch.Tensor, state_slots: torch.Tensor,
+             cu_seqlens: torch.Tensor, seq_index: torch.Tensor, num_seqs: int, dt_raw: torch.Tensor, dt_bias: torch.Tensor,
+             a_log: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Causal convolution per channel with silu, and the step sizes of a state-space layer.
+
+    xin [T, C] (a view, float32 or bfloat16); taps [C, K] and bias [C] float32 (the last tap weighs the
+    current token); conv_state: a float32 view [slots, >= (K-1)*C] whose row holds a request's last
+    K - 1 inputs [K-1, C], oldest first (read here for the tokens at a portion's start, and brought up
+    to date by a second launch).  dt_raw [T, H] float32, dt_bias, a_log [H] float32.
+    Returns (conv [T, C] float32, dt = softplus(dt_raw + dt_bias) [T, H], decay = exp(-exp(a_log) dt) [T, H])."""
+    flush_gemm_chain()
+    T, C = xin.shape
+    K, H = int(taps.shape[1]), int(dt_bias.numel())
+    _matrix_view("ssm_conv: xin", xin, T, C)
+    for name, t in (("taps", taps), ("bias", bias), ("dt_raw", dt_raw), ("dt_bias", dt_bias), ("a_log", a_log)):
+        _cuda_contig(name, t, torch.float32)
+    if taps.shape != (C, K) or bias.numel() != C or dt_raw.shape != (T, H) or a_log.numel() != H:
+        raise KernelError("ssm_conv: shapes disagree")
+    if (not conv_state.is_cuda or conv_state.dtype != torch.float32 or conv_state.dim() != 2 or conv_state.stride(1) != 1
+            or conv_state.shape[1] < (K - 1) * C):
+        raise KernelError("ssm_conv: conv_state must be a float32 view [slots, >= (taps - 1) * channels]")
+    out = torch.empty((T, C), device=xin.device, dtype=torch.float32)
+    dt = torch.empty((T, H), device=xin.device, dtype=torch.float32)
+    decay = torch.empty_like(dt)
+    code, stream = _act_code("xin", xin), _stream()
+    _check("ssm_conv", _fn("ts_ssm_conv")(
+        xin.data_ptr(), code, xin.stride(0), taps.data_ptr(), bias.data_ptr(), K, conv_state.data_ptr(), conv_state.stride(0),
+        state_slots.data_ptr(), cu_seqlens.data_ptr(), seq_index.data_ptr(), out.data_ptr(), T, C, dt_raw.data_ptr(), dt_bias.data_ptr(),
+        a_log.data_ptr(), dt.data_ptr(), decay.data_ptr(), H, stream))
+    if K > 1:
+        _check("ssm_conv", _fn("ts_ssm_conv_state")(xin.data_ptr(), code, xin.stride(0), K, conv_state.data_ptr(), conv_state.stride(0),
+                                                    state_slots.data_ptr(), cu_seqlens.data_ptr(), int(num_seqs), C, stream))
+    return out, dt, decay
+
+
+def ssm_gate_norm(o: torch.Tensor, x: torch.Tensor, skip: torch.Tensor, z: torch.Tensor, weight: torch.Tensor, out: torch.Tensor,
+                  num_heads: int, value_dim: int, parts: int, eps: float) -> None:
+    """y = (o + skip[h] * x) * silu(z), RMS-normed in `parts` equal parts of the row (each by its own root
+    mean square), times weight.  o [T, H*e] float32; x [T, H*e] float32 (a view); z (a view) and out
+    [T, H*e] in the compute type; skip [H] and weight [H*e] float32."""
+    H, e = int(num_heads), int(value_dim)
+    T = o.shape[0]
+    _cuda_contig("o", o, torch.float32)
+    _cuda_contig("skip", skip, torch.float32)
+    _cuda_contig("weight", weight, torch.float32)
+    _cuda_contig("out", out)
+    _matrix_view("ssm_gate_norm: x", x, T, H * e, torch.float32)
+    _matrix_view("ssm_gate_norm: z", z, T, H * e, out.dtype)
+    if o.shape != (T, H * e) or out.shape != (T, H * e) or weight.numel() != H * e or skip.numel() != H or parts < 1 or (H * e) % parts:
+        raise KernelError("ssm_gate_norm: shapes disagree")
+    _check("ssm_gate_norm", _fn("ts_ssm_gate_norm")(o.data_ptr(), x.data_ptr(), x.stride(0), skip.data_ptr(), z.data_ptr(), z.stride(0),
+                                                    _act_code("out", out), weight.data_ptr(), out.data_ptr(), T, H, e, int(parts), float(eps),
+                                                    _stream()))
+
+
+def scale_rows(x: torch.Tensor, factor: float) -> None:
+    """x *= factor in place, float32."""
+    flush_gemm_chain()
+    _cuda_contig("x", x, torch.float32)
+    _check("scale_rows", _fn("ts_scale_rows")(x.data_ptr(), x.numel(), float(factor), _stream()))
+
+
+WEIGHTED_SUM_MAX_INPUTS = 4
+
+
+def weighted_sum(inputs: "list[torch.Tensor]", scales: "list[float]", out: torch.Tensor) -> None:
+    """out = sum_j scales[j] * inputs[j], summed in float32 and rounded once; up to four inputs of
+    out's shape and type."""
+    flush_gemm_chain()
+    if not 1 <= len(inputs) <= WEIGHTED_SUM_MAX_INPUTS or len(inputs) != len(scales):
+        raise KernelError(f"weighted_sum: one to {WEIGHTED_SUM_MAX_INPUTS} inputs with a scale each")
+    _cuda_contig("out", out)
+    for t in inputs:
+        _cuda_contig("input", t, out.dtype)
+        if t.shape != out.shape:
+            raise KernelError("weighted_sum: shapes disagree")
+    ptrs = [t.data_ptr() for t in inputs] + [None] * (4 - len(inputs))
+    sc = [float(x) for x in scales] + [0.0] * (4 - len(inputs))
+    _check("weighted_sum", _fn("ts_weighted_sum")(*ptrs, *sc, len(inputs), out.data_ptr(), _act_code("out", out), out.numel(), _stream()))
+
+
+# ---------------------------------------------------------------------------
+# between a stacked q/k/v projection and attention, for mixers with biases, a rotation with a
+# magnitude, a unit norm after the rotation, or values of another width than keys
+
+QKV_PREPARE_MAX_DIM = 512
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float, num_tokens: int) -> torch.Tensor:
+    """[num_tokens, len(inv_freq), 2] float32: magnitude * (cos, sin)(positions[t] * inv_freq[j]), the
+    angle formed in float64 from float64 frequencies."""
+    _cuda_contig("positions", positions, torch.int32)
+    _cuda_contig("inv_freq", inv_freq, torch.float64)
+    if positions.numel() < num_tokens:
+        raise KernelError("rope_table: positions are shorter than the tokens")
+    half = inv_freq.numel()
+    out = torch.empty((num_tokens, half, 2), device=positions.device, dtype=torch.float32)
+    _check("rope_table", _fn("ts_rope_table")(positions.data_ptr(), inv_freq.data_ptr(), float(magnitude), num_tokens, half, out.data_ptr(),
+                                              _stream()))
+    return out
+
+
+def qkv_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor],
+                v_bias: Optional[torch.Tensor], table: Optional[torch.Tensor], unit_norm: bool, eps: float, q_out: torch.Tensor,
+                k_dst: Optional[torch.Tensor], v_dst: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor], num_heads: int,
+                num_kv_heads: int, key_dim: int, value_dim: int, padded_dim: int) -> None:
+    """Queries, keys and values of a step out of one projection's result `proj` [T, n] (columns q_off..,
+    k_off.., v_off..): biases [heads*dim] float32 (or None), rotation of the first 2*table.shape[1]
+    entries of every q and k head by the table's (cos, sin) (rope_table; None: no rotation), then with
+    `unit_norm` q and k heads divided by sqrt(mean(x^2) + eps).  q_out [T, nq, D]; keys and values go to
+    k_dst / v_dst [slots, nkv, D] at slot_mapping[t] (None: row t; a negative slot: not kept), padded with
+    zeros from their own width to D = padded_dim.  k_dst None: only the queries are made."""
+    flush_gemm_chain()
+    nq, nkv, d, e, D = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim), int(padded_dim)
+    T = proj.shape[0]
+    if not proj.is_cuda or proj.dim() != 2 or proj.stride(1) != 1:
+        raise KernelError("qkv_prepare: proj must be a CUDA matrix with unit inner stride")
+    if D > QKV_PREPARE_MAX_DIM or D < max(d, e):
+        raise KernelError(f"qkv_prepare: heads of {d} / {e} entries padded to {D}: at most {QKV_PREPARE_MAX_DIM}, at least the wider of the two")
+    _cuda_contig("q_out", q_out, proj.dtype)
+    if q_out.numel() != T * nq * D:
+        raise KernelError("qkv_prepare: q_out must be [T, heads, padded_dim]")
+    for name, t in (("q_bias", q_bias), ("k_bias", k_bias), ("v_bias", v_bias)):
+        if t is not None:
+            _cuda_contig(name, t, torch.float32)
+    rot = 0
+    if table is not None:
+        _cuda_contig("table", table, torch.float32)
+        if table.dim() != 3 or table.shape[0] < T or table.shape[2] != 2 or 2 * table.shape[1] > d:
+            raise KernelError(f"qkv_prepare: the table must be [T, rot/2, 2] with rot <= {d}, got {tuple(table.shape)}")
+        rot = 2 * table.shape[1]
+    kv_heads = nkv
+    if k_dst is None:
+        kv_heads = 0
+    else:
+        _cuda_contig("k_dst", k_dst, proj.dtype)
+        _cuda_contig("v_dst", v_dst, proj.dtype)
+        if tuple(k_dst.shape[-2:]) != (nkv, D) or tuple(v_dst.shape[-2:]) != (nkv, D):
+            raise KernelError(f"qkv_prepare: k_dst and v_dst must end in [{nkv}, {D}], got {tuple(k_dst.shape)} and {tuple(v_dst.shape)}")
+    if slot_mapping is not None:
+        _cuda_contig("slot_mapping", slot_mapping, torch.int32)
+    _check("qkv_prepare", _fn("ts_qkv_prepare")(
+        proj.data_ptr(), _act_code("proj", proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
+        _ptr(table), rot, 1 if unit_norm else 0, float(eps), q_out.data_ptr(), _ptr(k_dst), _ptr(v_dst), _ptr(slot_mapping), T, nq, kv_heads,
+        d, e, D, _stream()))
+
+
+def gate_rows(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, num_heads: int, value_dim: int, padded_dim: int) -> None:
+    """out[t, h*e + i] = a[t, h, i] * sigmoid(gate[t, h*e + i]); a [T, H, D] with D >= e (the entries
+    beyond e are dropped); gate None: the compaction alone."""
+    H, e, D = int(num_heads), int(value_dim), int(padded_dim)
+    _cuda_contig("a", a)
+    _cuda_contig("out", out, a.dtype)
+    T = out.shape[0]
+    if a.numel() != T * H * D or out.shape != (T, H * e):
+        raise KernelError("gate_rows: shapes disagree")
+    if gate is not None:
+        _matrix_view("gate_rows: gate", gate, T, H * e, a.dtype)
+    _check("gate_rows", _fn("ts_gate_rows")(a.data_ptr(), _ptr(gate), 0 if gate is None else gate.stride(0), _act_code("a", a), out.data_ptr(),
+                                            T, H, e, D, _stream()))
 
 
 ROTARY_PAIRINGS = {"half": 0, "neighbours": 1}

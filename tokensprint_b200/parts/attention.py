@@ -44,6 +44,18 @@ class AttentionMixer(Mixer):
     `chunk` = n: a query sees only the keys of its own block of n positions (blocks count from
     position 0 of the sequence); the cache gives the pages of earlier blocks back.
     `sink` = s: every softmax's denominator also holds exp(s), a key without a value.
+    `sinks` = name of a [num_heads] tensor: the same with a learned score per query head.
+    `softcap` = c > 0: the scaled score passes through c * tanh(s / c) before the softmax.
+    `q_bias`, `k_bias`, `v_bias`: names of the projections' biases.
+    `qk_norm` = "unit_after_rotation": q and k heads are divided by sqrt(mean(x^2) + qk_norm_eps)
+    after the rotation, without a weight.
+    `value_dim`: values (and the heads the output projection reads) of another width than keys.
+    `gate` = name of a [num_heads * value_dim, hidden] matrix: the concatenated heads are multiplied
+    by sigmoid(gate x) before the output projection.
+    A position encoding whose cosines and sines carry a magnitude is applied from its table.
+    With any of the options from `sinks` on, one product gives [q | k | v | gate], `qkv_prepare`
+    adds biases, rotates, norms and stores (keys and values padded with zeros to one common width
+    that the attention kernels take), and the gate is a kernel behind attention.
     """
 
     folds_norms = True
@@ -73,11 +85,25 @@ class AttentionMixer(Mixer):
         values: str = "projection",
         chunk: int = 0,
         sink: Optional[float] = None,
+        sinks: Optional[str] = None,
+        softcap: float = 0.0,
+        q_bias: Optional[str] = None,
+        k_bias: Optional[str] = None,
+        v_bias: Optional[str] = None,
+        value_dim: Optional[int] = None,
+        gate: Optional[str] = None,
     ) -> None:
         if qk_norm is True:
             qk_norm = "head"
-        if qk_norm not in (False, "head", "joint"):
-            raise ValueError(f"attention: qk_norm must be False, 'head' or 'joint', got {qk_norm!r}")
+        if qk_norm not in (False, "head", "joint", "unit_after_rotation"):
+            raise ValueError(f"attention: qk_norm must be False, 'head', 'joint' or 'unit_after_rotation', got {qk_norm!r}")
+        unit_after = qk_norm == "unit_after_rotation"
+        if unit_after:
+            qk_norm = False
+        if sink is not None and sinks is not None:
+            raise ValueError("attention: one sink score for all heads, or a tensor of scores, not both")
+        if softcap < 0:
+            raise ValueError("attention: softcap must not be negative")
         if values not in ("projection", "keys"):
             raise ValueError(f"attention: values must be 'projection' or 'keys', got {values!r}")
         if (values == "projection") != (v is not None):
@@ -98,40 +124,71 @@ class AttentionMixer(Mixer):
         if self.chunk < 0:
             raise ValueError("attention: chunk must not be negative")
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
-        self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm}
+        self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm, "sinks": sinks, "q_bias": q_bias,
+                      "k_bias": k_bias, "v_bias": v_bias, "gate": gate}
         self.position = build_part("position_encoding", position, ctx) if position is not None else None
+        self.unit_after_rotation, self.softcap = unit_after, float(softcap)
+        self.value_dim = self.head_dim if value_dim is None else int(value_dim)
+        magnitude = getattr(self.position, "magnitude", 1.0) if self.position is not None else 1.0
+        # the path through qkv_prepare (see the class's text)
+        self.general = bool(unit_after or sinks or softcap or q_bias or k_bias or v_bias or gate or self.value_dim != self.head_dim
+                            or magnitude != 1.0)
+        # the width the attention kernels run at: the wider of keys and values, and in bfloat16 the next
+        # multiple of 16 (what the tensor-core kernels take): entries beyond a head's own are zeros
+        self.kernel_dim = self.head_dim
+        if self.general:
+            if self.joint_norm or self.qk_norm or self.values_are_keys:
+                raise ValueError("attention: biases, a unit norm after the rotation, a gate, learned sinks, a score cap and values of "
+                                 "another width come without the weighted q/k norms and with a value projection")
+            if self.position is not None and not hasattr(self.position, "rotary_table"):
+                raise ValueError("attention: these options take a rotation that offers its table of cosines and sines (or none)")
+            self.kernel_dim = max(self.head_dim, self.value_dim)
+            if ctx.dtype == torch.bfloat16:
+                self.kernel_dim = -(-self.kernel_dim // 16) * 16
+            if self.kernel_dim > ops.QKV_PREPARE_MAX_DIM:
+                raise ValueError(f"attention: heads of at most {ops.QKV_PREPARE_MAX_DIM} entries, got {self.kernel_dim}")
         # the kernels of this mixer read everything a step needs from device memory; a position
         # encoding that rewrites q and k itself decides for itself
         self.graph_safe = self.position is None or self.position.graph_safe
-        if self.joint_norm:
+        if self.joint_norm or self.general:
             self.folds_norms = False  # its q/k kernel is a step of its own
-            if self.position is not None and self.position.rotary_inv_freq() is None:
+            if self.joint_norm and self.position is not None and self.position.rotary_inv_freq() is None:
                 raise ValueError("attention: the joint q/k norm takes a rotate-half rotation (or none)")
         self.dtype = ctx.dtype
         self.qkv_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None
         self.q_norm_weight: Optional[torch.Tensor] = None
         self.k_norm_weight: Optional[torch.Tensor] = None
+        self.head_sinks: Optional[torch.Tensor] = None
+        self.biases: dict[str, Optional[torch.Tensor]] = {"q": None, "k": None, "v": None}
 
     def first_weight(self) -> Optional[torch.Tensor]:
         return self.qkv_weight
 
     def cache_need(self) -> CacheNeed:
         if self.window > 0:  # (a layer with both bounds keeps what its window needs)
-            return CacheNeed(kind="window", window=self.window, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+            return CacheNeed(kind="window", window=self.window, kv_heads=self.num_kv_heads, head_dim=self.kernel_dim)
         if self.chunk > 0:
-            return CacheNeed(kind="chunk", window=self.chunk, kv_heads=self.num_kv_heads, head_dim=self.head_dim)
-        return CacheNeed(kind="full", kv_heads=self.num_kv_heads, head_dim=self.head_dim)
+            return CacheNeed(kind="chunk", window=self.chunk, kv_heads=self.num_kv_heads, head_dim=self.kernel_dim)
+        return CacheNeed(kind="full", kv_heads=self.num_kv_heads, head_dim=self.kernel_dim)
 
     def tensor_specs(self) -> list[TensorSpec]:
-        H, nq, nkv, d = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        H, nq, nkv, d, e = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        n = self.names
         specs = [
             TensorSpec(self.names["q"], (nq * d, H)),
             TensorSpec(self.names["k"], (nkv * d, H)),
-            TensorSpec(self.names["o"], (H, nq * d)),
+            TensorSpec(self.names["o"], (H, nq * e)),
         ]
         if not self.values_are_keys:
-            specs.insert(2, TensorSpec(self.names["v"], (nkv * d, H)))
+            specs.insert(2, TensorSpec(self.names["v"], (nkv * e, H)))
+        if n["gate"] is not None:
+            specs.append(TensorSpec(n["gate"], (nq * e, H)))
+        if n["sinks"] is not None:
+            specs.append(TensorSpec(n["sinks"], (nq,), "vector"))
+        for key, width in (("q_bias", nq * d), ("k_bias", nkv * d), ("v_bias", nkv * e)):
+            if n[key] is not None:
+                specs.append(TensorSpec(n[key], (width,), "vector"))
         if self.qk_norm:
             specs.append(TensorSpec(self.names["q_norm"], (nq * d if self.joint_norm else d,), "vector"))
             specs.append(TensorSpec(self.names["k_norm"], (nkv * d if self.joint_norm else d,), "vector"))
@@ -142,7 +199,14 @@ class AttentionMixer(Mixer):
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
         stacked = [tensors[n["q"]], tensors[n["k"]]] + ([] if self.values_are_keys else [tensors[n["v"]]])
+        if n["gate"] is not None:
+            stacked.append(tensors[n["gate"]])
         self.qkv_weight = torch.cat(stacked, dim=0).contiguous()
+        if n["sinks"] is not None:
+            self.head_sinks = tensors[n["sinks"]]
+        for key in ("q", "k", "v"):
+            if n[key + "_bias"] is not None:
+                self.biases[key] = tensors[n[key + "_bias"]]
         self.o_weight = tensors[n["o"]]
         if self.qk_norm:
             self.q_norm_weight = tensors[n["q_norm"]]
@@ -166,6 +230,8 @@ class AttentionMixer(Mixer):
         q = torch.empty((T, nq * d), device=xt.device, dtype=xt.dtype)
         if self.joint_norm:
             return self._forward_joint(x, q, step, cache, tables)
+        if self.general:
+            return self._forward_general(x, step, cache, tables)
         inv_freq = self.position.rotary_inv_freq() if self.position is not None else None
         fused = self.position is None or inv_freq is not None
         if (fused and cache.writes and d == ops.GEMM_QK_ROPE_HEAD_DIM and (inv_freq is None or inv_freq.numel() == d // 2)
@@ -217,11 +283,35 @@ class AttentionMixer(Mixer):
         self._attend(q, out, step, cache, tables)
         return linear(out, self.o_weight, next_weight=step.weight_after)
 
+    def _forward_general(self, x, step: StepContext, cache: LayerCache, tables):
+        """One product for [q | k | v | gate]; biases, rotation from the table, the unit norm and the
+        stores in one kernel (keys and values padded to the kernels' width); attention; the gate
+        (and the cut back to the values' own width); the output product."""
+        T = x.shape[0]
+        nq, nkv, d, e, D = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim, self.kernel_dim
+        proj = linear(x, self.qkv_weight, next_weight=self.o_weight)
+        table = self.position.rotary_table(step) if self.position is not None else None
+        q = torch.empty((T, nq * D), device=x.device, dtype=x.dtype)
+        k_off, v_off, g_off = nq * d, nq * d + nkv * d, nq * d + nkv * d + nkv * e
+        writes = cache.writes
+        ops.qkv_prepare(proj, 0, k_off, v_off, self.biases["q"], self.biases["k"], self.biases["v"], table, self.unit_after_rotation,
+                        self.qk_norm_eps, q, cache.k_pages if writes else None, cache.v_pages if writes else None,
+                        tables.slot_mapping if writes else None, nq, nkv, d, e, D)
+        out = torch.empty((T, nq * D), device=x.device, dtype=x.dtype)
+        self._attend(q, out, step, cache, tables)
+        gated = self.names["gate"] is not None
+        if gated or D != e:
+            y = torch.empty((T, nq * e), device=x.device, dtype=x.dtype)
+            ops.gate_rows(out, proj[:, g_off:g_off + nq * e] if gated else None, y, nq, e, D)
+            out = y
+        return linear(out, self.o_weight, next_weight=step.weight_after)
+
     # -- attention proper ---------------------------------------------------
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
-        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
-        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.kernel_dim
+        plain_scores = self.softcap == 0.0 and self.head_sinks is None  # (what the tensor-core kernels know)
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d) and plain_scores:
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
             if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
@@ -255,12 +345,13 @@ class AttentionMixer(Mixer):
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
             q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
-            step.page_size, self.num_heads, self.num_kv_heads, self.head_dim, self.scale, self.window, self.chunk, self.sink)
+            step.page_size, self.num_heads, self.num_kv_heads, d, self.scale, self.window, self.chunk, self.sink,
+            softcap=self.softcap, head_sinks=self.head_sinks)
 
     def _attend_decode(self, q, out, step: StepContext, cache: LayerCache, tables, first: int, count: int, max_q: int) -> None:
         """Sequences [first, first + count) of the batch, each with at most `max_q` tokens (few enough
         rows for the decode kernels); q and out hold exactly their tokens."""
-        nq, nkv, d = self.num_heads, self.num_kv_heads, self.head_dim
+        nq, nkv, d = self.num_heads, self.num_kv_heads, self.kernel_dim
         cu = step.cu_seqlens_q[first : first + count + 1]
         lens = step.context_lens[first : first + count]
         table = tables.block_table[first : first + count]

@@ -29,16 +29,19 @@ class PreNormBlock(Block):
 
     The residual stream is float32.  Each branch output is handed on as `pending` and
     added by the next norm in the same pass that norms it, so a residual sum never costs
-    a pass over memory of its own.
+    a pass over memory of its own.  A layer without a feed-forward ends with its mixer.
     """
 
-    def __init__(self, ctx: BuildContext, *, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, ffn_norm: PartSpec) -> None:
+    def __init__(self, ctx: BuildContext, *, mixer: PartSpec, mixer_norm: PartSpec, feed_forward: Optional[PartSpec] = None,
+                 ffn_norm: Optional[PartSpec] = None) -> None:
+        if (feed_forward is None) != (ffn_norm is None):
+            raise ValueError("pre_norm block: a feed-forward and its norm come together")
         self.dtype = ctx.dtype
         self.mixer = build_part("mixer", mixer, ctx)
-        self.feed_forward = build_part("feed_forward", feed_forward, ctx)
+        self.feed_forward = None if feed_forward is None else build_part("feed_forward", feed_forward, ctx)
         self.mixer_norm = build_part("norm", mixer_norm, ctx)
-        self.ffn_norm = build_part("norm", ffn_norm, ctx)
-        self._parts = (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward)
+        self.ffn_norm = None if ffn_norm is None else build_part("norm", ffn_norm, ctx)
+        self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.feed_forward) if p is not None)
         self.graph_safe = all(p.graph_safe for p in self._parts)
         # the block itself only hands tensors on; before a part that reads them by other means
         # than this package's ops, products that still wait in a chain are launched
@@ -67,7 +70,7 @@ class PreNormBlock(Block):
             pending = None
         after_block, norm_after = step.weight_after, step.norm_after
         mixer_folds = self.mixer.folds_norms and self.mixer.can_fold(T, self.dtype)
-        ffn_folds = self.feed_forward.folds_norms and self.feed_forward.can_fold(T, self.dtype)
+        ffn_folds = self.feed_forward is not None and self.feed_forward.folds_norms and self.feed_forward.can_fold(T, self.dtype)
 
         if isinstance(pending, PreNormed) and mixer_folds:
             x = pending
@@ -77,6 +80,9 @@ class PreNormBlock(Block):
             x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
             self._before(self.mixer_norm)
             self.mixer_norm.forward(hidden, None if isinstance(pending, PreNormed) else pending, x)
+        if self.feed_forward is None:
+            self._before(self.mixer)
+            return self.mixer.forward(x, step, cache)
         step.weight_after = self.feed_forward.first_weight()
         ffn_norm = self.ffn_norm.params()
         self._before(self.mixer)

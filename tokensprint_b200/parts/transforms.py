@@ -81,3 +81,18 @@ class PassEntry(Transform):
             raise ops.KernelError("pass_entry: the embedding rows were not kept for this step")
         ops.stream_add(x, embedding if self.add_embedding else None, self.vector)
         return x
+
+
+@register_part("transform", "scale")
+class Scale(Transform):
+    """x <- factor * x in float32: a constant on the logits (or on the embedding rows)."""
+
+    graph_safe = True
+    reads_through_ops = True
+
+    def __init__(self, ctx: BuildContext, *, factor: float) -> None:
+        self.factor = float(factor)
+
+    def forward(self, x: torch.Tensor, step: Optional[StepContext]) -> torch.Tensor:
+        ops.scale_rows(x, self.factor)
+        return x
