@@ -145,12 +145,13 @@ def capped_attention(h: torch.Tensor, positions: Sequence[int], m: dict, prefix:
             freq, magnitude = base_frequencies(float(rot["base"]), int(rot["dims"])), 1.0
         q, k = rotate_halves(q, positions, freq, magnitude), rotate_halves(k, positions, freq, magnitude)
     q, k = unit_rms(q, eps), unit_rms(k, eps)
-    cap = float(m["softcap"])
+    cap = float(m["softcap"]) if m.get("softcap") else None
     out = torch.empty(T, H, e, dtype=dt)
     for head in range(H):
         g = head // (H // G)
         scores = (q[:, head] @ k[:, g].T) * float(m["scale"])
-        scores = cap * torch.tanh(scores / cap)
+        if cap is not None:
+            scores = cap * torch.tanh(scores / cap)
         out[:, head] = causal_weights(scores) @ v[:, g]
     gate = torch.sigmoid(h @ w("g").T)
     return (out.reshape(T, H * e) * gate) @ w("o").T
