@@ -204,16 +204,31 @@ def _paged(rows, page, dtype, seed):
     return _dev(pool), order.to(torch.int32)
 
 
-def _attend(q, k, v, q_pos, page, nq, nkv, d, scale, softcap, sinks, dtype, seed=0):
-    """One sequence: keys 0..N-1 in the cache, queries at `q_pos` (the last ones of the sequence)."""
+def _attend(q, k, v, q_pos, page, nq, nkv, d, scale, softcap, sinks, dtype, seed=0, kernel="simple", splits=1):
+    """One sequence: keys 0..N-1 in the cache, queries at `q_pos`.  "simple": the CUDA-core kernel, any
+    positions; "mma" and "tcgen05" (bfloat16): the tensor-core kernels, whose queries are the last
+    len(q_pos) positions of a sequence of q_pos[-1] + 1 tokens; `splits` > 1: the keys over several CTAs."""
     from tokensprint_b200 import ops
 
     kp, table = _paged(k, page, dtype, seed)
     vp, _ = _paged(v, page, dtype, seed)
     T = len(q_pos)
     out = torch.empty((T, nq * d), device="cuda", dtype=dtype)
-    ops.attention_paged_simple(_dev(q.reshape(T, nq * d).to(dtype)), kp, vp, out, _i32(q_pos), _i32([0] * T), _dev(table).view(1, -1), page,
-                               nq, nkv, d, scale, softcap=softcap, head_sinks=None if sinks is None else _dev(sinks.float()))
+    qd, hs = _dev(q.reshape(T, nq * d).to(dtype)), None if sinks is None else _dev(sinks.float())
+    if kernel == "simple":
+        ops.attention_paged_simple(qd, kp, vp, out, _i32(q_pos), _i32([0] * T), _dev(table).view(1, -1), page, nq, nkv, d, scale,
+                                   softcap=softcap, head_sinks=hs)
+    else:
+        assert list(q_pos) == list(range(q_pos[-1] + 1 - T, q_pos[-1] + 1))
+        cu, lens = _i32([0, T]), _i32([q_pos[-1] + 1])
+        if kernel == "tcgen05":
+            ops.attention_prefill_tcgen05(qd, kp, vp, out, cu, lens, _dev(table).view(1, -1), page, 1, T, nq, nkv, scale, 0, softcap=softcap,
+                                          head_sinks=hs)
+        else:
+            scratch = torch.empty(ops.attention_scratch_floats(T * nq, splits, d), device="cuda", dtype=torch.float32) if splits > 1 else None
+            ops.attention_paged_mma(qd, kp, vp, out, cu, lens, _dev(table).view(1, -1), _i32([0] * T), page, 1, T, nq, nkv, d, scale, 0, splits,
+                                    scratch, 0, softcap=softcap, head_sinks=hs)
+        ops.check_device_errors()
     return out.float().cpu().reshape(T, nq, d)
 
 
@@ -246,6 +261,32 @@ def test_capped_scores_and_sinks_random(dtype, nq, nkv, d, page, softcap, with_s
     assert _rel(got, want) < TOL[dtype]
 
 
+@pytest.mark.parametrize("nq, nkv, d, page, softcap, with_sinks", [(4, 2, 32, 8, 7.0, False), (3, 1, 16, 16, 0.0, True), (6, 6, 64, 32, 15.0, True),
+                                                                   (2, 1, 128, 16, 30.0, False), (8, 2, 128, 64, 0.0, True), (4, 4, 128, 16, 10.0, True),
+                                                                   (5, 5, 48, 64, 4.0, True), (16, 2, 64, 16, 25.0, True)])
+def test_capped_scores_and_sinks_on_tensor_cores(nq, nkv, d, page, softcap, with_sinks):
+    """The tensor-core kernels (bfloat16): a prompt portion behind a kept prefix (the prompt kernels: mma, and
+    tcgen05 at heads of 128), and single decoded tokens with the keys over 1 to 8 CTAs (the sink is
+    counted once, the cap applies in every range), against the plain softmax."""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(nq * d + 1)
+    N = 333
+    q, k, v = (torch.randn(N, h, d, generator=g).to(dtype).float() for h in (nq, nkv, nkv))
+    sinks = torch.randn(nq, generator=g) * 2 if with_sinks else None
+    scale = 1.5 / math.sqrt(d)
+    want = _plain_attend(q, k, v, list(range(N)), nq, nkv, scale, softcap, sinks)
+    kernels = ["mma"] + (["tcgen05"] if d == 128 and page >= 8 and (64 % page == 0 or page % 128 == 0) else [])
+    for kernel in kernels:
+        for first in (0, 100, 331):  # whole; behind a prefix; the last two tokens
+            q_pos = list(range(first, N))
+            got = _attend(q[first:], k, v, q_pos, page, nq, nkv, d, scale, softcap, sinks, dtype, kernel=kernel)
+            assert _rel(got, want[first:]) < TOL[dtype], f"{kernel}, queries from {first}: {_rel(got, want[first:]):.3g}"
+    for n in (1, 40, 333):
+        for splits in (1, 2, 5, 8):
+            got = _attend(q[n - 1:n], k[:n], v[:n], [n - 1], page, nq, nkv, d, scale, softcap, sinks, dtype, kernel="mma", splits=splits)
+            assert _rel(got, want[n - 1:n]) < TOL[dtype], f"decode at {n} keys, {splits} splits: {_rel(got, want[n - 1:n]):.3g}"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_one_far_key_among_hundreds_and_the_first_key(dtype):
     """A query that matches one key hundreds of positions back (at a page's last slot, at a page's
@@ -260,10 +301,12 @@ def test_one_far_key_among_hundreds_and_the_first_key(dtype):
         q = torch.zeros(1, nq, d)
         q[0, :, 3] = 6.0
         for softcap in (0.0, 20.0):
-            got = _attend(q, kk.to(dtype).float(), v.to(dtype).float(), [N - 1], page, nq, nkv, d, 1.0, softcap, None, dtype, seed=far)
             want = _plain_attend(q, kk.to(dtype).float(), v.to(dtype).float(), [N - 1], nq, nkv, 1.0, softcap, None)
-            assert _rel(got, want) < TOL[dtype]
-            assert float((got[0, 0] - v[far, 0].to(dtype).float()).abs().max()) < 0.05, f"key {far} was not found (cap {softcap})"
+            for kernel, splits in [("simple", 1)] + ([("mma", 1), ("mma", 4)] if dtype == torch.bfloat16 else []):
+                got = _attend(q, kk.to(dtype).float(), v.to(dtype).float(), [N - 1], page, nq, nkv, d, 1.0, softcap, None, dtype, seed=far,
+                              kernel=kernel, splits=splits)
+                assert _rel(got, want) < TOL[dtype]
+                assert float((got[0, 0] - v[far, 0].to(dtype).float()).abs().max()) < 0.05, f"key {far} was not found (cap {softcap}, {kernel})"
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

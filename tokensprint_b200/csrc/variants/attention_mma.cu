@@ -47,6 +47,12 @@ constexpr unsigned TMA_SPIN_LIMIT = 1u << 22;
 #endif
 constexpr int TSTAGES = TS_DECODE_TMA_STAGES;           // key blocks in flight per CTA on the copy-engine path
 
+// Builds with TS_ATT_SCORED=1 also know a sink score per query head and a tanh cap on the scores; the others
+// carry none of that code (their callers are refused both).
+#ifndef TS_ATT_SCORED
+#define TS_ATT_SCORED 0
+#endif
+constexpr bool SCORED = TS_ATT_SCORED != 0;
 struct AttnParams {
   const __nv_bfloat16* q;         // [T, nq, D]
   const __nv_bfloat16* kcache;    // [slots, nkv, D]
@@ -68,6 +74,11 @@ struct AttnParams {
   int chunk;                      // > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from position 0)
   int has_sink;                   // 1: every softmax's denominator also holds exp(sink score): a key without a value
   float sink_raw;                 // the sink's score divided by the scale (the running max is kept in raw score units)
+#if TS_ATT_SCORED
+  const float* head_sinks;        // [nq] one sink score per query head (has_sink is then 1 and sink_raw unused), or null
+  float inv_scale;                // 1 / scale (a head's sink score in raw units)
+  float cap_raw, cap_inv;         // cap / scale and scale / cap: a raw score s becomes cap_raw * tanh(s * cap_inv); cap_raw 0: no cap
+#endif
   int* flat_prefix;               // even-share kernel: [B + 1] key blocks of the sequences before each one, left for its combine kernel
 };
 
@@ -83,6 +94,30 @@ __device__ __forceinline__ int first_visible_key(const AttnParams& p, int pos) {
   int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
   if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
   return lo;
+}
+// The sink score, in raw units, of row `r` of a (sequence, KV head) pair's rows (row r belongs to query head hk * G + r % G).
+__device__ __forceinline__ float row_sink_raw(const AttnParams& p, int hk, int G, int r) {
+#if TS_ATT_SCORED
+  if (p.head_sinks != nullptr) return p.head_sinks[hk * G + r % G] * p.inv_scale;
+#endif
+  return p.sink_raw;
+}
+__device__ __forceinline__ bool has_cap(const AttnParams& p) {
+#if TS_ATT_SCORED
+  return p.cap_raw > 0.f;
+#else
+  return false;
+#endif
+}
+// Scores bent through a tanh cap, still in raw units: tanh(x) = 1 - 2 / (exp(2x) + 1), exact at both ends
+// (exp overflows to inf: 1; underflows to 0: -1), absolute error of a few 1e-7 in between.
+__device__ __forceinline__ float capped_score(const AttnParams& p, float s) {
+#if TS_ATT_SCORED
+  const float t = __expf(2.f * s * p.cap_inv);
+  return p.cap_raw * (1.f - __fdividef(2.f, t + 1.f));
+#else
+  return s;
+#endif
 }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -492,7 +527,8 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     // The sink is a key of a fixed score and no value: exactly one of the partial softmaxes of a row
     // starts from it (the first split's; of warps that share rows, the first warp's), and every merge
     // downstream takes it along.  A row's sum is spread over the four threads of a quad: one of them holds it.
-    m_run[0] = m_run[1] = p.sink_raw;
+    m_run[0] = row_sink_raw(p, hk, G, r0 + warp_row0 + g);
+    m_run[1] = row_sink_raw(p, hk, G, r0 + warp_row0 + g + 8);
     l_run[0] = l_run[1] = tq == 0 ? 1.f : 0.f;
   }
 
@@ -576,6 +612,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     // so it commutes with max) and the scale is folded into the exponent's multiply-add:
     // p = 2^(s * scale - max * scale).  Blocks that every valid row of this warp sees in full
     // skip the mask; the output is rescaled only when some row's max moved.
+    if (has_cap(p)) {
+#pragma unroll
+      for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[nt][e] = capped_score(p, s[nt][e]);
+    }
     float m_new[2] = {m_run[0], m_run[1]};
     const int wk0 = kbase + key0;  // first key this warp scores in this block
     const bool unmasked = (wk0 + NTILES * 8 - 1 <= warp_min_pos) && (wk0 >= warp_max_lo);
@@ -923,7 +965,9 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
   float m_run[PF_MT][2], l_run[PF_MT][2];
 #pragma unroll
   for (int mt = 0; mt < PF_MT; ++mt) {
-    m_run[mt][0] = m_run[mt][1] = p.has_sink ? p.sink_raw : -INFINITY;  // the sink: a key of a fixed score and no value
+    // the sink: a key of a fixed score and no value
+    m_run[mt][0] = p.has_sink ? row_sink_raw(p, hk, G, r0 + warp_row0 + mt * 16 + g) : -INFINITY;
+    m_run[mt][1] = p.has_sink ? row_sink_raw(p, hk, G, r0 + warp_row0 + mt * 16 + g + 8) : -INFINITY;
     l_run[mt][0] = l_run[mt][1] = (p.has_sink && tq == 0) ? 1.f : 0.f;       // (a row's sum is spread over a quad's threads)
   }
   const __nv_bfloat16* q_warp = q_s + warp_row0 * LD;
@@ -973,6 +1017,14 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
     // inside every row's window, and whose rows all exist needs no mask.
     const bool unmasked = warp_rows_valid && (kbase + BN - 1 <= warp_first_pos) &&
                           kbase >= first_visible_key(p, start_pos + (r0 + warp_row0 + 16 * PF_MT - 1) / G);
+    if (has_cap(p)) {
+#pragma unroll
+      for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) s[mt][nt][e] = capped_score(p, s[mt][nt][e]);
+    }
 #pragma unroll
     for (int mt = 0; mt < PF_MT; ++mt) {
       // Running max in raw score units (the scale is positive, so it commutes with max); the
@@ -1781,14 +1833,18 @@ TS_EXPORT int ts_attention_mma_last_launches(void) { return ts_attention_last_la
 
 // `chunk` > 0: queries see only the keys of their own block of `chunk` positions; `has_sink`: exp(sink_score)
 // joins every softmax's denominator.  (The even-share decode kernel below knows neither.)
-TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, const void* vcache, void* out,
+// `softcap` > 0: the scaled score passes through softcap * tanh(score / softcap); `head_sinks` [nq]: a sink score per
+// query head (instead of `sink_score`).
+TS_EXPORT int ts_attention_paged_mma_scored(const void* q, const void* kcache, const void* vcache, void* out,
                                             float* scratch, const int* cu_q, const int* ctx_len,
                                             const int* block_table, const int* seq_index, int max_blocks,
                                             int page, int T, int B, int max_q, int nq, int nkv, float scale,
-                                            int window, int chunk, int has_sink, float sink_score, int splits, int keys_per_split,
-                                            int* counters, void* stream_) {
+                                            int window, int chunk, int has_sink, float sink_score, float softcap, const float* head_sinks,
+                                            int splits, int keys_per_split, int* counters, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
-  if (chunk < 0 || (has_sink && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
+  if (!SCORED && (head_sinks != nullptr || softcap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (head_sinks != nullptr) has_sink = 1;
+  if (chunk < 0 || ((has_sink || softcap > 0.f) && !(scale > 0.f)) || softcap < 0.f) return TS_ERR_BAD_ARGUMENT;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1 ||
       keys_per_split < 0 || keys_per_split % BN != 0)
     return TS_ERR_BAD_ARGUMENT;
@@ -1814,6 +1870,12 @@ TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, c
   p.chunk = chunk;
   p.has_sink = has_sink ? 1 : 0;
   p.sink_raw = has_sink ? sink_score / scale : 0.f;
+#if TS_ATT_SCORED
+  p.head_sinks = head_sinks;
+  p.inv_scale = (has_sink || softcap > 0.f) ? 1.f / scale : 0.f;
+  p.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
+  p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+#endif
   p.splits = splits;
   p.keys_per_split = keys_per_split;
   p.counters = (counters != nullptr && splits > 1 && (long long)max_q * (nq / nkv) <= 16) ? counters : nullptr;
@@ -1847,6 +1909,17 @@ TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, c
     status = ts_launch(attention_combine_kernel, dim3((total + 3) / 4), dim3(128), 0, stream, (const float*)p.part_o, (const float*)p.part_ml, p.out, seq_index, total, nq, splits);
   }
   return status;
+}
+
+TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, const void* vcache, void* out,
+                                            float* scratch, const int* cu_q, const int* ctx_len,
+                                            const int* block_table, const int* seq_index, int max_blocks,
+                                            int page, int T, int B, int max_q, int nq, int nkv, float scale,
+                                            int window, int chunk, int has_sink, float sink_score, int splits, int keys_per_split,
+                                            int* counters, void* stream_) {
+  return ts_attention_paged_mma_scored(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index, max_blocks, page, T, B,
+                                       max_q, nq, nkv, scale, window, chunk, has_sink, sink_score, 0.f, nullptr, splits, keys_per_split,
+                                       counters, stream_);
 }
 
 TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,

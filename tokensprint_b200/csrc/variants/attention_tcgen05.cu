@@ -53,6 +53,12 @@ constexpr int MAX_TABLE = 1024;                   // block-table entries kept in
 constexpr uint32_t TMEM_COLS = 256;               // S: 64 columns, O_blk: 128 columns
 constexpr uint32_t TMEM_S = 0, TMEM_O = 64;
 
+// Builds with TS_ATT_SCORED=1 also know a sink score per query head and a tanh cap on the scores; the others
+// carry none of that code (their callers are refused both).
+#ifndef TS_ATT_SCORED
+#define TS_ATT_SCORED 0
+#endif
+constexpr bool SCORED = TS_ATT_SCORED != 0;
 struct Params {
   __nv_bfloat16* out;     // [T, nq, D]
   const int* cu_q;        // [B + 1]
@@ -63,6 +69,11 @@ struct Params {
   int chunk;        // > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from position 0)
   int has_sink;     // 1: every softmax's denominator also holds exp(sink score): a key without a value
   float sink_raw;   // the sink's score divided by the scale (the running max is kept in raw score units)
+#if TS_ATT_SCORED
+  const float* head_sinks;  // [nq] one sink score per query head (has_sink is then 1 and sink_raw unused), or null
+  float inv_scale;          // 1 / scale (a head's sink score in raw units)
+  float cap_raw, cap_inv;   // cap / scale and scale / cap: a raw score s becomes cap_raw * tanh(s * cap_inv); cap_raw 0: no cap
+#endif
   float scale_log2;
   long long* probe;  // TS_ATT_PROBE builds: clock stamps of CTA 0's first softmax warp and of its MMA thread
 };
@@ -178,6 +189,30 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
       : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
         "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
+}
+// The sink score, in raw units, of row `r` of a (sequence, KV head) pair's rows (row r belongs to query head hk * G + r % G).
+__device__ __forceinline__ float row_sink_raw(const Params& p, int hk, int G, int r) {
+#if TS_ATT_SCORED
+  if (p.head_sinks != nullptr) return p.head_sinks[hk * G + r % G] * p.inv_scale;
+#endif
+  return p.sink_raw;
+}
+__device__ __forceinline__ bool has_cap(const Params& p) {
+#if TS_ATT_SCORED
+  return p.cap_raw > 0.f;
+#else
+  return false;
+#endif
+}
+// Scores bent through a tanh cap, still in raw units: tanh(x) = 1 - 2 / (exp(2x) + 1), exact at both ends
+// (exp overflows to inf: 1; underflows to 0: -1), absolute error of a few 1e-7 in between.
+__device__ __forceinline__ float capped_score(const Params& p, float s) {
+#if TS_ATT_SCORED
+  const float t = __expf(2.f * s * p.cap_inv);
+  return p.cap_raw * (1.f - __fdividef(2.f, t + 1.f));
+#else
+  return s;
+#endif
 }
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
@@ -331,7 +366,7 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
 #pragma unroll
   for (int i = 0; i < D; ++i) o[i] = 0.f;
   // (with a sink the row's softmax starts from it: a key of a fixed score and no value)
-  float m_run = p.has_sink ? p.sink_raw : -INFINITY, l_run = p.has_sink ? 1.f : 0.f;
+  float m_run = p.has_sink ? row_sink_raw(p, hk, G, r) : -INFINITY, l_run = p.has_sink ? 1.f : 0.f;
   const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 
   // A wait that gives up raises abort_s; the CTA leaves the loop together at the next barrier.
@@ -354,6 +389,10 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
       for (int i = 0; i < 16; ++i) s[c * 16 + i] = __uint_as_float(v[i]);
     }
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+    if (has_cap(p)) {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) s[j] = capped_score(p, s[j]);
+    }
 
     // every key of the block is seen by every row of the tile that belongs to a token (rows that belong
     // to nobody need no mask: a row's result depends on that row alone, and theirs is never stored)
@@ -817,7 +856,7 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
     const uint32_t o_addr = lane_addr + 256 + t * 128 + h * 64;  // its half of the row of O
     // l_run: the sum over this thread's keys only; with a sink both threads of a row start from its score
     // and one of them holds its share of the sum
-    float m_run = p.has_sink ? p.sink_raw : -INFINITY, l_run = (p.has_sink && h == 0) ? 1.f : 0.f;
+    float m_run = p.has_sink ? row_sink_raw(p, hk, G, r) : -INFINITY, l_run = (p.has_sink && h == 0) ? 1.f : 0.f;
     bool ok = true;
 
     for (int blk = 0; blk < nblocks; ++blk) {
@@ -837,6 +876,17 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
         tmem_ld32(s_addr, v0);
         tmem_ld32(s_addr + 32, v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (has_cap(p)) {
+          // the capped scores take the raw ones' place in tensor memory: the second walk reads them from there
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            v0[i] = __float_as_uint(capped_score(p, __uint_as_float(v0[i])));
+            v1[i] = __float_as_uint(capped_score(p, __uint_as_float(v1[i])));
+          }
+          tmem_st32(s_addr, v0);
+          tmem_st32(s_addr + 32, v1);
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
         float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};  // four chains: the warp has few others to hide latency behind
         if (unmasked) {
 #pragma unroll
@@ -1063,13 +1113,17 @@ TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
 // `mode`: 0 chooses by the longest portion (two tiles per CTA when a sequence has more than 128
 // rows), 1 one tile per CTA, 2 two tiles per CTA.
 // `error`: one int the kernel sets to 1 if one of its waits gave up.
-TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, const void* vcache, void* out,
-                                           const int* cu_q, const int* ctx_len, const int* block_table,
-                                           int max_blocks, int page, long long total_slots, int T, int B, int max_q,
-                                           int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
-                                           int mode, int* error, void* stream_) {
+// `softcap` > 0: the scaled score passes through softcap * tanh(score / softcap); `head_sinks` [nq]: a sink score per
+// query head (instead of `sink_score`).
+TS_EXPORT int ts_attention_prefill_tcgen05_scored(const void* q, const void* kcache, const void* vcache, void* out,
+                                                  const int* cu_q, const int* ctx_len, const int* block_table,
+                                                  int max_blocks, int page, long long total_slots, int T, int B, int max_q,
+                                                  int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
+                                                  float softcap, const float* head_sinks, int mode, int* error, void* stream_) {
   if (T <= 0 || B <= 0) return 0;
-  if (chunk < 0 || (has_sink && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
+  if (!SCORED && (head_sinks != nullptr || softcap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (head_sinks != nullptr) has_sink = 1;
+  if (chunk < 0 || ((has_sink || softcap > 0.f) && !(scale > 0.f)) || softcap < 0.f) return TS_ERR_BAD_ARGUMENT;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
     return TS_ERR_BAD_ARGUMENT;
   if (total_slots > 0x7fffffffLL - page || ((long long)max_q * (nq / nkv) / ((BM / (nq / nkv)) * (nq / nkv)) + 1) * nkv * B > 0x7fffffffLL) return TS_ERR_UNSUPPORTED_SIZE;
@@ -1088,6 +1142,12 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   p.chunk = chunk;
   p.has_sink = has_sink ? 1 : 0;
   p.sink_raw = has_sink ? sink_score / scale : 0.f;
+#if TS_ATT_SCORED
+  p.head_sinks = head_sinks;
+  p.inv_scale = (has_sink || softcap > 0.f) ? 1.f / scale : 0.f;
+  p.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
+  p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
+#endif
   p.total_slots = (int)total_slots;
   p.num_seqs = B;
   p.scale_log2 = scale * 1.4426950408889634f;
@@ -1124,4 +1184,13 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
   }
   return ts_launch(attention_tcgen05_kernel, dim3((unsigned)(((rows + RT - 1) / RT) * nkv * B)), dim3(128), smem, (cudaStream_t)stream_, mq, mk,
                    mv, p);
+}
+
+TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, const void* vcache, void* out,
+                                           const int* cu_q, const int* ctx_len, const int* block_table,
+                                           int max_blocks, int page, long long total_slots, int T, int B, int max_q,
+                                           int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
+                                           int mode, int* error, void* stream_) {
+  return ts_attention_prefill_tcgen05_scored(q, kcache, vcache, out, cu_q, ctx_len, block_table, max_blocks, page, total_slots, T, B, max_q,
+                                             nq, nkv, scale, window, chunk, has_sink, sink_score, 0.f, nullptr, mode, error, stream_);
 }

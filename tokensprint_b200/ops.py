@@ -1483,15 +1483,20 @@ def attention_mma_supported(head_dim: int) -> bool:
     return head_dim % 16 == 0 and 16 <= head_dim <= ATTENTION_MMA_MAX_HEAD_DIM
 
 
-def _attention_mma_fns(head_dim: int):
-    fns = _attention_mma.get(head_dim)
+def _attention_mma_fns(head_dim: int, scored: bool = False):
+    """(run, scratch_floats) of the library built for `head_dim`; `scored`: the build that also knows a
+    sink score per query head and a tanh cap on the scores (a library of its own, so that the kernels
+    of models without either carry none of that code)."""
+    key = (head_dim, True) if scored else head_dim
+    fns = _attention_mma.get(key)
     if fns is None:
         if not attention_mma_supported(head_dim):
             raise KernelError(
                 f"attention_paged_mma: head_dim must be a multiple of 16 between 16 and {ATTENTION_MMA_MAX_HEAD_DIM}, got {head_dim}")
-        lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim})
-        run = lib.ts_attention_paged_mma_masked
-        run.argtypes = [_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_void_p, _c_void_p]
+        lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim, "TS_ATT_SCORED": 1} if scored else {"TS_HEAD_DIM": head_dim})
+        run = lib.ts_attention_paged_mma_scored
+        run.argtypes = ([_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_int, _c_int,
+                                                         _c_void_p, _c_void_p])
         run.restype = _c_int
         scratch = lib.ts_attention_mma_scratch_floats
         scratch.argtypes = [_c_ll, _c_int]
@@ -1512,9 +1517,12 @@ def _attention_mma_fns(head_dim: int):
         lib.ts_attention_mma_decode_slots.restype = _c_ll
         lib.ts_attention_mma_decode_rows.restype = _c_int
         lib.ts_attention_mma_last_launches.restype = _c_int
-        _attention_flat[head_dim] = lib
+        if scored:
+            _attention_scored[head_dim] = lib
+        else:
+            _attention_flat[head_dim] = lib
         fns = (run, scratch)
-        _attention_mma[head_dim] = fns
+        _attention_mma[key] = fns
     return fns
 
 
@@ -1619,6 +1627,8 @@ def attention_paged_mma(
     fuse_merge: bool = True,
     chunk: int = 0,
     sink: Optional[float] = None,
+    softcap: float = 0.0,
+    head_sinks: Optional[torch.Tensor] = None,
 ) -> None:
     """Causal attention over the paged cache on tensor cores (bfloat16).
 
@@ -1630,10 +1640,17 @@ def attention_paged_mma(
     0 divides each sequence's keys evenly.  In decode steps the last CTA of each (sequence, KV
     head) pair merges the pair's splits itself (`fuse_merge`); otherwise a second kernel does.
     chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from
-    position 0); sink: a score that joins every softmax's denominator without a value.
+    position 0); sink: a score that joins every softmax's denominator without a value; head_sinks
+    [nq] float32: one such score per query head; softcap > 0: the scaled score goes through
+    softcap * tanh(s / softcap).
     """
     flush_gemm_chain()
-    run, _ = _attention_mma_fns(head_dim)
+    scored = head_sinks is not None or softcap > 0.0
+    run, _ = _attention_mma_fns(head_dim, scored)
+    if head_sinks is not None:
+        _cuda_contig("head_sinks", head_sinks, torch.float32)
+        if head_sinks.numel() != num_heads or sink is not None:
+            raise KernelError(f"attention: head_sinks must have one entry per query head ({num_heads}) and come without `sink`")
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
         _cuda_contig(name, t, torch.bfloat16)
     for name, t in (("cu_seqlens_q", cu_seqlens_q), ("context_lens", context_lens), ("block_table", block_table), ("seq_index", seq_index)):
@@ -1665,10 +1682,11 @@ def attention_paged_mma(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), _ptr(scratch),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
         block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(chunk),
-        0 if sink is None else 1, 0.0 if sink is None else float(sink), int(splits), int(keys_per_split), counters, _stream()))
+        0 if sink is None else 1, 0.0 if sink is None else float(sink), float(softcap), _ptr(head_sinks), int(splits), int(keys_per_split),
+        counters, _stream()))
     if splits > 1:
         global launch_count
-        launch_count += _attention_flat[d].ts_attention_mma_last_launches() - 1  # the combine kernel, if one ran
+        launch_count += (_attention_scored if scored else _attention_flat)[d].ts_attention_mma_last_launches() - 1  # the combine kernel, if one ran
 
 
 # Decode steps whose (sequence, KV head) pairs times key splits do not all run at once go to the
@@ -1677,6 +1695,7 @@ ATTENTION_DECODE_FLAT = _os.environ.get("TS_ATTENTION_FLAT", "1") != "0"
 ATTENTION_FLAT_MAX_SEQS = 512
 ATTENTION_FLAT_MAX_ROWS = 16
 _attention_flat: dict[int, ctypes.CDLL] = {}
+_attention_scored: dict[int, ctypes.CDLL] = {}  # the builds with per-head sinks and a score cap
 _flat_ctas: dict[int, int] = {}
 
 
@@ -1788,15 +1807,26 @@ def attention_scratch_floats(rows: int, splits: int, head_dim: int) -> int:
 
 ATTENTION_TCGEN05_HEAD_DIM = 128
 _attention_tcgen05 = None
+_attention_tcgen05_scored = None  # the build with per-head sinks and a score cap
 _USE_ATTENTION_TCGEN05 = _os.environ.get("TS_ATTENTION_TCGEN05", "1") != "0"
 
 
-def _attention_tcgen05_fns():
-    global _attention_tcgen05
+def _attention_tcgen05_fns(scored: bool = False):
+    global _attention_tcgen05, _attention_tcgen05_scored
+    if scored:
+        if _attention_tcgen05_scored is None:
+            _attention_tcgen05_fns()
+            lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM, "TS_ATT_SCORED": 1})
+            run = lib.ts_attention_prefill_tcgen05_scored
+            run.argtypes = _attention_tcgen05[0].argtypes
+            run.restype = _c_int
+            _attention_tcgen05_scored = (run, _attention_tcgen05[1])
+        return _attention_tcgen05_scored
     if _attention_tcgen05 is None:
         lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM})
-        run = lib.ts_attention_prefill_tcgen05
-        run.argtypes = [_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p, _c_void_p]
+        run = lib.ts_attention_prefill_tcgen05_scored
+        run.argtypes = ([_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p,
+                                                                                     _c_int, _c_void_p, _c_void_p])
         run.restype = _c_int
         ok = lib.ts_attention_tcgen05_supported
         ok.argtypes = [_c_int, _c_int, _c_int]
@@ -1834,6 +1864,8 @@ def attention_prefill_tcgen05(
     mode: int = 0,
     chunk: int = 0,
     sink: Optional[float] = None,
+    softcap: float = 0.0,
+    head_sinks: Optional[torch.Tensor] = None,
 ) -> None:
     """Causal attention of prompt portions over the paged cache, tcgen05 tensor cores, head size 128.
 
@@ -1842,7 +1874,7 @@ def attention_prefill_tcgen05(
     their own, 0 chooses by the longest portion.
     """
     flush_gemm_chain()
-    run, ok = _attention_tcgen05_fns()
+    run, ok = _attention_tcgen05_fns(head_sinks is not None or softcap > 0.0)
     d = ATTENTION_TCGEN05_HEAD_DIM
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
         _cuda_contig(name, t, torch.bfloat16)
@@ -1862,13 +1894,17 @@ def attention_prefill_tcgen05(
         raise KernelError("attention_prefill_tcgen05: block_table must be [B,max_blocks]")
     if cu_seqlens_q.numel() < num_seqs + 1 or context_lens.numel() < num_seqs:
         raise KernelError("attention_prefill_tcgen05: cu_seqlens_q/context_lens are shorter than the batch")
+    if head_sinks is not None:
+        _cuda_contig("head_sinks", head_sinks, torch.float32)
+        if head_sinks.numel() != nq or sink is not None:
+            raise KernelError(f"attention_prefill_tcgen05: head_sinks must have one entry per query head ({nq}) and come without `sink`")
     _, error = _gemm_workspace(q.device)
     _check("attention_prefill_tcgen05", run(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, k_cache.shape[0] * page_size, T, num_seqs, max_seqlen_q, nq, nkv,
-        float(scale), int(window), int(chunk), 0 if sink is None else 1, 0.0 if sink is None else float(sink), int(mode),
-        error.data_ptr(), _stream()))
+        float(scale), int(window), int(chunk), 0 if sink is None else 1, 0.0 if sink is None else float(sink), float(softcap),
+        _ptr(head_sinks), int(mode), error.data_ptr(), _stream()))
 
 
 # ---------------------------------------------------------------------------

@@ -310,8 +310,8 @@ class AttentionMixer(Mixer):
 
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.kernel_dim
-        plain_scores = self.softcap == 0.0 and self.head_sinks is None  # (what the tensor-core kernels know)
-        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d) and plain_scores:
+        scored = {"softcap": self.softcap, "head_sinks": self.head_sinks}
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
             if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
@@ -329,18 +329,19 @@ class AttentionMixer(Mixer):
                 ops.attention_prefill_tcgen05(
                     q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q[singles:], step.context_lens[singles:],
                     tables.block_table[singles:], step.page_size, B - singles, step.max_seqlen_q, nq, nkv, self.scale, self.window,
-                    chunk=self.chunk, sink=self.sink)
+                    chunk=self.chunk, sink=self.sink, **scored)
                 return
             if prompts_on_tcgen05:
                 # prompt portions: the tcgen05 kernel, where it takes the sizes
                 ops.attention_prefill_tcgen05(
                     q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
-                    step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, self.scale, self.window, chunk=self.chunk, sink=self.sink)
+                    step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, self.scale, self.window, chunk=self.chunk, sink=self.sink,
+                    **scored)
                 return
             ops.attention_paged_mma(
                 q, cache.k_pages, cache.v_pages, out, step.cu_seqlens_q, step.context_lens, tables.block_table,
                 step.seq_index, step.page_size, step.num_seqs, step.max_seqlen_q, nq, nkv, d, self.scale,
-                self.window, 1, None, 0, chunk=self.chunk, sink=self.sink)
+                self.window, 1, None, 0, chunk=self.chunk, sink=self.sink, **scored)
             return
         # float32 runs, and head sizes the tensor-core kernel does not take
         ops.attention_paged_simple(
@@ -362,8 +363,9 @@ class AttentionMixer(Mixer):
         reach = min(self.window, self.chunk) if self.window and self.chunk else self.window or self.chunk  # the most keys a query sees
         context = ops.attention_decode_plan_context(step.max_context_len, reach)
         splits = ops.attention_decode_splits(count, nkv, context, d)
-        # (the even-share decode kernel knows neither a block bound nor a sink)
-        if (self.chunk == 0 and self.sink is None and ops.attention_decode_prefers_flat(count, nkv, splits, d)
+        # (the even-share decode kernel knows neither a block bound nor a sink nor a score cap)
+        if (self.chunk == 0 and self.sink is None and self.head_sinks is None and self.softcap == 0.0
+                and ops.attention_decode_prefers_flat(count, nkv, splits, d)
                 and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, count, max_q)):
             # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
             ops.attention_decode_flat(
@@ -375,7 +377,7 @@ class AttentionMixer(Mixer):
             scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d), device=q.device, dtype=torch.float32)
         ops.attention_paged_mma(
             q, cache.k_pages, cache.v_pages, out, cu, lens, table, seq_index, step.page_size, count, max_q, nq, nkv, d,
-            self.scale, self.window, splits, scratch, 0, chunk=self.chunk, sink=self.sink)
+            self.scale, self.window, splits, scratch, 0, chunk=self.chunk, sink=self.sink, softcap=self.softcap, head_sinks=self.head_sinks)
 
     # -- less common paths ----------------------------------------------------
 
