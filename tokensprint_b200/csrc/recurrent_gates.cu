@@ -5,7 +5,7 @@
 //
 // rows_dot_f32:      out[t, r] = x[t, :] . w[r, :] + bias[r] with float32 weights and sums: the few
 //                    rows of a projection that feed gates or step sizes (a bfloat16 result would
-//                    carry three digits into an exponential).  One warp per (token, row).
+//                    carry three digits into an exponential).  One warp per (token, 8 rows).
 // mlstm_gate_scan:   per (sequence, head), from the gates' pre-activations pre[t] = (i~, f~):
 //                      log_i = cap tanh(i~ / cap),  log_f = logsigmoid(cap tanh(f~ / cap))
 //                      m_t = max(log_f + m_(t-1), log_i)        m before a request's first token is 0
@@ -29,40 +29,49 @@ __device__ __forceinline__ float rg_log_sigmoid(float z) { return fminf(z, 0.f) 
 __device__ __forceinline__ float rg_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float rg_silu(float z) { return z / (1.f + expf(-z)); }
 
+#define RD_ROWS 8  // weight rows a warp carries per pass over its token's row
+
 template <typename TA>
 __global__ void rows_dot_f32_kernel(const TA* __restrict__ x, long long ld_x, const float* __restrict__ w, const float* __restrict__ bias,
                                     float* __restrict__ out, int T, int R, int W) {
   ts_pdl_prologue();
-  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  // One warp per (token, block of RD_ROWS weight rows): every entry of the token's row is read once per block and meets
+  // RD_ROWS weights; the warps of a CTA take consecutive tokens of the same block, so the weights stay in L1.
   const int lane = threadIdx.x & 31;
-  if (item >= (long long)T * R) return;
-  const int t = (int)(item / R), r = (int)(item - (long long)t * R);
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int r0 = blockIdx.y * RD_ROWS;
+  if (t >= T) return;
   const TA* xr = x + (size_t)t * ld_x;
-  const float* wr = w + (size_t)r * W;
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  int i = lane;
-  for (; i + 96 < W; i += 128) {
-    acc[0] = fmaf(ts_to_float(xr[i]), wr[i], acc[0]);
-    acc[1] = fmaf(ts_to_float(xr[i + 32]), wr[i + 32], acc[1]);
-    acc[2] = fmaf(ts_to_float(xr[i + 64]), wr[i + 64], acc[2]);
-    acc[3] = fmaf(ts_to_float(xr[i + 96]), wr[i + 96], acc[3]);
+  const float* wr[RD_ROWS];
+#pragma unroll
+  for (int j = 0; j < RD_ROWS; ++j) wr[j] = w + (size_t)min(r0 + j, R - 1) * W;  // (rows beyond the last repeat it and are not stored)
+  float acc[RD_ROWS];
+#pragma unroll
+  for (int j = 0; j < RD_ROWS; ++j) acc[j] = 0.f;
+  for (int i = lane; i < W; i += 32) {
+    const float xv = ts_to_float(xr[i]);
+#pragma unroll
+    for (int j = 0; j < RD_ROWS; ++j) acc[j] = fmaf(xv, wr[j][i], acc[j]);
   }
-  for (; i < W; i += 32) acc[0] = fmaf(ts_to_float(xr[i]), wr[i], acc[0]);
-  const float sum = ts_warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-  if (lane == 0) out[(size_t)t * R + r] = sum + (bias ? bias[r] : 0.f);
+#pragma unroll
+  for (int j = 0; j < RD_ROWS; ++j) {
+    const float sum = ts_warp_sum(acc[j]);
+    if (lane == 0 && r0 + j < R) out[(size_t)t * R + r0 + j] = sum + (bias ? bias[r0 + j] : 0.f);
+  }
 }
 
 TS_EXPORT int ts_rows_dot_f32(const void* x, int act_dtype, long long ld_x, const float* w, const float* bias, float* out, int T, int R, int W,
                               void* stream) {
   if (T <= 0 || R <= 0) return 0;
   if (W <= 0) return TS_ERR_BAD_ARGUMENT;
-  const long long items = (long long)T * R;
-  const unsigned blocks = (unsigned)((items + 3) / 4);
+  const int row_blocks = (R + RD_ROWS - 1) / RD_ROWS;
+  if (row_blocks > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+  const dim3 grid((unsigned)((T + 3) / 4), (unsigned)row_blocks);
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    return ts_launch(rows_dot_f32_kernel<float>, dim3(blocks), dim3(128), 0, s, (const float*)x, ld_x, w, bias, out, T, R, W);
+    return ts_launch(rows_dot_f32_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ld_x, w, bias, out, T, R, W);
   if (act_dtype == TS_DTYPE_BF16)
-    return ts_launch(rows_dot_f32_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, s, (const __nv_bfloat16*)x, ld_x, w, bias, out, T, R, W);
+    return ts_launch(rows_dot_f32_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x, ld_x, w, bias, out, T, R, W);
   return TS_ERR_BAD_ARGUMENT;
 }
 

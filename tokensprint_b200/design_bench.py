@@ -10,6 +10,12 @@ copy bandwidth).  `python bench.py --designs` prints one JSON line.
 with a sink, gated linear attention, routed SwiGLU experts, every sublayer between two norms)
 beside Qwen3 dense at equal width, depth, heads and feed-forward weight per token, and adds the
 recurrent mixer's and the norm kernels' distance from their rooflines.
+
+`python bench.py --designs pekunex` runs Pekunex (attention with a score cap, a gate and biases;
+attention with a sink per head beside a matrix memory; a state-space layer; dense SwiGLU) beside
+Dazilix, the closest design the engine has (attention with a sink and a linear recurrence), at equal
+width, depth, heads and feed-forward weight per token, with the distance of Pekunex's attention,
+recurrence and small kernels from their rooflines next to the like kernels of Dazilix.
 """
 
 from __future__ import annotations
@@ -82,6 +88,75 @@ def qwen3_beside_dazilix(s: dict) -> dict:
             "num_attention_heads": s["heads"], "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": inter, "vocab_size": VOCAB,
             "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False, "max_position_embeddings": 8192,
             "hidden_act": "silu", "attention_bias": False, "torch_dtype": "bfloat16"}
+
+
+# Pekunex at the same widths: a capped attention, the pair side by side (attention with sinks beside a matrix memory whose
+# state is [heads, 64, 128 + 1] float32 per request), a state-space layer (inner width twice the model's, state 128) and a
+# second capped attention; heads of 128; a dense SwiGLU of the weight per token of Dazilix's chosen experts.
+PEKUNEX_SIZES = {
+    "w2048": dict(width=2048, heads=16, layers=4, ff=2048, mem_dim=64, mem_vdim=128, ssm_heads=64, ssm_vdim=64, ssm_state=128, ssm_groups=8),
+    "w4096": dict(width=4096, heads=32, layers=4, ff=6144, mem_dim=64, mem_vdim=128, ssm_heads=128, ssm_vdim=64, ssm_state=128, ssm_groups=8),
+}
+
+
+def pekunex_config(s: dict) -> dict:
+    att = {"heads": s["heads"], "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 1.0, "softcap": 30.0,
+           "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    left = {"heads": s["heads"], "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+            "rot": {"base": 1000000.0, "dims": 128, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 4096}}}
+    right = {"heads": s["heads"], "dim": s["mem_dim"], "vdim": s["mem_vdim"], "gate_cap": 15.0}
+    ssm = {"heads": s["ssm_heads"], "vdim": s["ssm_vdim"], "state": s["ssm_state"], "groups": s["ssm_groups"], "conv": 4, "norm_groups": 8}
+    mlp = {"kind": "dense", "ff": s["ff"]}
+    return {"architecture": "Pekunex", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0}, "logit_scale": 1.0,
+            "layers": [{"type": "attention", "mixer": att, "mlp": mlp},
+                       {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 1.0, "right_scale": 1.0}, "mlp": mlp},
+                       {"type": "mamba2", "mixer": ssm, "mlp": mlp}, {"type": "attention", "mixer": att, "mlp": mlp}]}
+
+
+def dazilix_beside_pekunex(s: dict) -> dict:
+    d = next(v for k, v in DAZILIX_SIZES.items() if v["width"] == s["width"])
+    return dazilix_config(d)
+
+
+def _pekunex_rooflines(s: dict, m: dict, peaks: dict) -> dict[str, Any]:
+    """Pekunex's recurrences and small kernels against their rooflines, from the per-class timers.  The
+    recurrence (both mixers run the same kernel): a prompt costs 6 float32 operations per state entry and
+    token against the FFMA rate of the SMs at their top clock; a decode step reads and writes every
+    request's states once, against the measured copy bandwidth.  The kernels between the projections
+    and attention (biases, rotation, unit norm, store; the gate behind attention) and around the
+    recurrences (convolution, gates, norms) move their inputs and outputs once, against the same."""
+    out: dict[str, Any] = {}
+    H, d, e = s["heads"], s["mem_dim"], s["mem_vdim"] + 1
+    Hs, N, es, G = s["ssm_heads"], s["ssm_state"], s["ssm_vdim"], s["ssm_groups"]
+    entries = H * d * e + Hs * N * es  # state entries of one request, both recurrent layers
+    ffma_peak = 148 * 128 * 2 * peaks.get("sm_max_mhz", 1965.0) * 1e6
+    hbm = peaks["hbm_gbs"] * 1e9
+    T, W = PREFILL_TOKENS, s["width"]
+    inner, chans = Hs * es, Hs * es + 2 * G * N
+    # bytes per token of the small kernels (bf16 in and out unless float32 is named)
+    small = {
+        "qkv_prepare": 3 * 2 * (H + 16) * 128 * 2,                                  # three attentions: q, k, v read and written
+        "gate_rows": 2 * 3 * H * 128 * 2,                                              # two gated attentions: heads, gate, result
+        "ssm_conv": chans * 2 + chans * 4 + 3 * Hs * 4,                                # inputs bf16, outputs float32, step sizes and decays
+        "ssm_gate_norm": inner * (4 + 4 + 2 + 2),                                      # read-out and x float32, z and result bf16
+        "mlstm_norm_gate": H * e * 4 + 2 * H * (e - 1) * 2,                            # read-out float32, gate and result bf16
+        "weighted_sum": 3 * W * 2,
+    }
+    for phase, kernels, tokens in [("prefill", m["prefill_kernels"], T)] + [(f"decode_b{b}", m[f"decode_b{b}_kernels"], b) for b in DECODE_BATCHES]:
+        ms = kernels.get("linear_scan", {}).get("ms", 0.0)
+        if ms > 0:
+            out[f"{phase}_linear_scan_ms"] = round(ms, 4)
+            if phase == "prefill":
+                out["prefill_linear_scan_of_ffma_peak"] = round(6.0 * T * entries / (ms * 1e-3) / ffma_peak, 3)
+            else:
+                out[f"{phase}_linear_scan_of_hbm_peak"] = round(tokens * entries * 8 / (ms * 1e-3) / hbm, 3)
+        for name, per_token in small.items():
+            ms = kernels.get(name, {}).get("ms", 0.0)
+            if ms > 0:
+                out[f"{phase}_{name}_ms"] = round(ms, 4)
+                if phase == "prefill":
+                    out[f"prefill_{name}_of_hbm_peak"] = round(tokens * per_token / (ms * 1e-3) / hbm, 3)
+    return out
 
 
 def _random_ids(n: int, seed: int) -> list[int]:
@@ -176,6 +251,11 @@ def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str
         names = ("latent_attention_mma",)
         flops = L * 2 * H * pairs * (576 + 512)
         row_bytes = 576 * 2
+    elif design == "pekunex":
+        L = 3  # two capped attentions and the attention of the pair
+        names = ("attention_prefill_tcgen05", "attention_paged_mma")
+        flops = L * 4 * H * 128 * pairs
+        row_bytes = 2 * 8 * 128 * 2
     elif design == "dazilix":
         L = s["layers"] - len(DAZILIX_RECURRENT_LAYERS)
         names = ("attention_prefill_tcgen05", "attention_paged_mma")
@@ -248,18 +328,25 @@ def run(steps: int, warmup: int, peaks: dict, which: str = "fegetar") -> dict[st
 
     result: dict[str, Any] = {"metric": "design_comparison", "dtype": "bf16", "data": "synthetic, random weights",
                               "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT, "sizes": {}}
-    sizes = DAZILIX_SIZES if which == "dazilix" else SIZES
+    sizes = {"dazilix": DAZILIX_SIZES, "pekunex": PEKUNEX_SIZES}.get(which, SIZES)
     for name, s in sizes.items():
         row: dict[str, Any] = {"size": s}
-        pair = ((("dazilix", dazilix_config(s)), ("qwen3", qwen3_beside_dazilix(s))) if which == "dazilix" else
-                (("fegetar", fegetar_config(s)), ("qwen3", qwen3_config(s))))
+        if which == "pekunex":
+            pair = (("pekunex", pekunex_config(s)), ("dazilix", dazilix_beside_pekunex(s)))
+        elif which == "dazilix":
+            pair = (("dazilix", dazilix_config(s)), ("qwen3", qwen3_beside_dazilix(s)))
+        else:
+            pair = (("fegetar", fegetar_config(s)), ("qwen3", qwen3_config(s)))
         for design, cfg_dict in pair:
             cfg = architecture_for(cfg_dict).config_from_dict(cfg_dict)
             model = random_model(cfg, seed=1, device="cuda", dtype="bfloat16", generate_on_device=True)
             m = _measure(model, steps, warmup)
             m["weight_bytes"] = model.weight_bytes()
-            m.update(_attention_rooflines(design, s, m, peaks))
-            if which == "dazilix":
+            sd = DAZILIX_SIZES[name] if (which == "pekunex" and design == "dazilix") else s
+            m.update(_attention_rooflines(design, sd, m, peaks))
+            if which == "pekunex":
+                m.update(_pekunex_rooflines(s, m, peaks) if design == "pekunex" else _dazilix_rooflines(sd, m, peaks))
+            elif which == "dazilix":
                 m.update(_dazilix_rooflines(s, m, peaks) if design == "dazilix" else _qwen3_norm_roofline(s, m, peaks))
             row[design] = m
             del model

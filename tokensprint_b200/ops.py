@@ -2251,7 +2251,8 @@ _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu"
           "gemm_skinny_fused", "rope_cos_sin", "gemm_qk_rope_store", "library_mm", "sgemm_nt_batched", "library_bmm", "pair_hash_embed",
           "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "latent_attention_mma", "gelu_tanh", "capped_glu", "gelu_gate_rows",
           "router_topk", "router", "moe_plan", "moe_gate_up", "moe_down", "moe_combine", "branch_norm_add", "stream_add",
-          "qk_joint_norm_rope_store", "gla_scan", "gla_norm_gate")
+          "qk_joint_norm_rope_store", "gla_scan", "gla_norm_gate", "linear_scan", "rows_dot_f32", "mlstm_gate_scan", "mlstm_norm_gate",
+          "ssm_conv", "ssm_gate_norm", "scale_rows", "weighted_sum", "rope_table", "qkv_prepare", "gate_rows")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
 
