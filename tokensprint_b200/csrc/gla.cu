@@ -11,8 +11,8 @@
 // head reads them; worked out inside the scan they were computed once per block of value columns).
 //
 // gla_scan: one CTA per (sequence, head, block of value columns).  A thread owns one value column
-// and d / R consecutive key channels of it in registers (R lanes of a warp share a column and add
-// their partial outputs by shuffles).  The CTA walks its sequence's tokens of the step in order,
+// and d / R key channels of it in registers, in fours that interleave with those of the other lanes
+// (R lanes of a warp share a column and add their partial outputs by shuffles).  The CTA walks its sequence's tokens of the step in order,
 // up to GLA_TB at a time: q, k, the decay and v of those tokens are staged in shared memory by all
 // threads, then every thread runs the round's updates from there.
 // The state is read from the request's slot before the first token and written back after the
@@ -28,6 +28,13 @@
 #define GLA_THREADS 128
 #define GLA_PF 8         // staged q (k, z) entries a thread fetches ahead per round: tb * dp <= GLA_THREADS * GLA_PF
 #define GLA_PFV 4        // likewise for v: tb * cols <= GLA_THREADS * GLA_PFV
+#ifndef GLA_MIN_BLOCKS
+#define GLA_MIN_BLOCKS 1 // CTAs per SM the compiler plans the registers for
+#endif
+#ifndef GLA_UNROLL
+#define GLA_UNROLL 4     // tokens of a round whose loads and shuffles are in flight together
+#endif
+constexpr int GLA_UNROLL_TOKENS = GLA_UNROLL;
 
 __device__ __forceinline__ float gla_log_sigmoid(float z) {
   // log(1 / (1 + exp(-z))) without overflow on either side
@@ -59,7 +66,7 @@ __device__ __forceinline__ __nv_bfloat16 gla_load(const __nv_bfloat16* p) {
 // (S <- product * S + state), writes the read-outs, and the last segment writes the request's slot.
 // MODE 0 is the whole portion in one piece (decode steps, short portions: the same sums whatever the cut).
 template <typename TA, int KP, int MODE>
-__global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
+__global__ void __launch_bounds__(GLA_THREADS, GLA_MIN_BLOCKS) gla_scan_kernel(
     const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const float* __restrict__ decay,
     float q_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
     float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, int tb, int segs, int seg_len, float* __restrict__ seg_state,
@@ -82,7 +89,10 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   const int r = threadIdx.x % R, cj = threadIdx.x / R;  // lanes of one column sit side by side
   const int col = col0 + cj;
   const bool has_col = col < e;
-  const int c0 = r * KP;
+  // Register i of a thread holds key channel CH(i): its channels come in fours, and the fours of the R lanes of a column
+  // are interleaved (lane r owns fours r, r + R, r + 2 R, ...), so that the 16-byte loads of a warp's lanes fall on
+  // consecutive 16-byte pieces of the staged rows: no two of them meet in a bank of shared memory.
+#define CH(i) (((((i) >> 2) * R + r) << 2) + ((i) & 3))
   float* S = state + (size_t)state_slots[b] * slot_stride + ((size_t)h * d) * e;
   const size_t state_elems = (size_t)d * e;
   float* seg_L = MODE == 0 ? nullptr : seg_state + (((size_t)b * segs + seg) * H + h) * state_elems;   // this segment's end state
@@ -93,29 +103,29 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
   if (MODE == 0 || (seg == 0 && (MODE == 1 || last))) {
     // the request's state (MODE 2: only a sequence of one segment reads the slot, which it alone writes in this launch)
 #pragma unroll
-    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? S[(size_t)(c0 + i) * e + col] : 0.f;
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && CH(i) < d) ? S[(size_t)(CH(i)) * e + col] : 0.f;
     if (MODE == 1 && has_col) {
 #pragma unroll
       for (int i = 0; i < KP; ++i)
-        if (c0 + i < d) seg_S0[(size_t)(c0 + i) * e + col] = s_reg[i];
+        if (CH(i) < d) seg_S0[(size_t)(CH(i)) * e + col] = s_reg[i];
     }
   } else if (MODE == 1) {
 #pragma unroll
     for (int i = 0; i < KP; ++i) s_reg[i] = 0.f;
   } else if (seg == 0) {
 #pragma unroll
-    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? seg_S0[(size_t)(c0 + i) * e + col] : 0.f;
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && CH(i) < d) ? seg_S0[(size_t)(CH(i)) * e + col] : 0.f;
   } else {
     // what the segments before left, folded in order (the first one's end state already holds the request's state)
     const float* L = seg_state + (((size_t)b * segs) * H + h) * state_elems;
 #pragma unroll
-    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && c0 + i < d) ? L[(size_t)(c0 + i) * e + col] : 0.f;
+    for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && CH(i) < d) ? L[(size_t)(CH(i)) * e + col] : 0.f;
     for (int j = 1; j < seg; ++j) {
       L = seg_state + (((size_t)b * segs + j) * H + h) * state_elems;
       const float* P = seg_decay + (((size_t)b * segs + j) * H + h) * d;
 #pragma unroll
       for (int i = 0; i < KP; ++i)
-        if (has_col && c0 + i < d) s_reg[i] = fmaf(P[c0 + i], s_reg[i], L[(size_t)(c0 + i) * e + col]);
+        if (has_col && CH(i) < d) s_reg[i] = fmaf(P[CH(i)], s_reg[i], L[(size_t)(CH(i)) * e + col]);
     }
   }
   if (MODE == 1) {
@@ -188,17 +198,17 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     stage(t0);
     __syncthreads();
     if (t0 + tb < t_end) fetch(t0 + tb);  // in flight while this round's updates run
-#pragma unroll(KP > 16 ? 1 : 4)  // several tokens' loads and shuffles in flight where the registers allow
+#pragma unroll(KP > 16 ? 1 : GLA_UNROLL_TOKENS)  // several tokens' loads and shuffles in flight where the registers allow
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = sv[tt * cols_per_cta + cj];
-      // a thread's KP channels are a multiple of four and start on a 16-byte boundary: 16-byte loads
-      const float4* pq = reinterpret_cast<const float4*>(sq + tt * dp + c0);
-      const float4* pk = reinterpret_cast<const float4*>(sk + tt * dp + c0);
-      const float4* pa = reinterpret_cast<const float4*>(sa + tt * dp + c0);
+      // a thread's channels come in fours that start on 16-byte boundaries: 16-byte loads
+      const float4* pq = reinterpret_cast<const float4*>(sq + tt * dp) + r;
+      const float4* pk = reinterpret_cast<const float4*>(sk + tt * dp) + r;
+      const float4* pa = reinterpret_cast<const float4*>(sa + tt * dp) + r;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};  // four chains: the read-out is a sum of KP terms, its order is fixed by KP alone
 #pragma unroll
       for (int i = 0; i < KP / 4; ++i) {
-        const float4 a4 = pa[i], k4 = pk[i];
+        const float4 a4 = pa[i * R], k4 = pk[i * R];
         s_reg[4 * i + 0] = fmaf(a4.x, s_reg[4 * i + 0], k4.x * vv);
         s_reg[4 * i + 1] = fmaf(a4.y, s_reg[4 * i + 1], k4.y * vv);
         s_reg[4 * i + 2] = fmaf(a4.z, s_reg[4 * i + 2], k4.z * vv);
@@ -209,7 +219,7 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
           p_reg[(MODE == 1 ? 4 * i + 2 : 0)] *= a4.z;
           p_reg[(MODE == 1 ? 4 * i + 3 : 0)] *= a4.w;
         } else {
-          const float4 q4 = pq[i];
+          const float4 q4 = pq[i * R];
           acc[0] = fmaf(s_reg[4 * i + 0], q4.x, acc[0]);
           acc[1] = fmaf(s_reg[4 * i + 1], q4.y, acc[1]);
           acc[2] = fmaf(s_reg[4 * i + 2], q4.z, acc[2]);
@@ -227,19 +237,21 @@ __global__ void __launch_bounds__(GLA_THREADS) gla_scan_kernel(
     if (has_col) {
 #pragma unroll
       for (int i = 0; i < KP; ++i)
-        if (c0 + i < d) seg_L[(size_t)(c0 + i) * e + col] = s_reg[i];
+        if (CH(i) < d) seg_L[(size_t)(CH(i)) * e + col] = s_reg[i];
     }
     if (blockIdx.z == 0 && cj == 0) {  // the decays do not depend on the column: one thread per group of channels writes them
 #pragma unroll
       for (int i = 0; i < KP; ++i)
-        if (c0 + i < d) seg_P[c0 + i] = p_reg[MODE == 1 ? i : 0];
+        if (CH(i) < d) seg_P[CH(i)] = p_reg[MODE == 1 ? i : 0];
     }
   } else if (has_col && (MODE == 0 || last)) {
 #pragma unroll
     for (int i = 0; i < KP; ++i)
-      if (c0 + i < d) S[(size_t)(c0 + i) * e + col] = s_reg[i];
+      if (CH(i) < d) S[(size_t)(CH(i)) * e + col] = s_reg[i];
   }
 }
+
+#undef CH
 
 // What the general form of the recurrence has beyond gated linear attention's (see ts_linear_scan).
 struct GlaExtra {
