@@ -5,8 +5,8 @@
 //
 // rows_dot_f32:      out[t, r] = x[t, :] . w[r, :] + bias[r] with float32 weights and sums: the few
 //                    rows of a projection that feed gates or step sizes (a bfloat16 result would
-//                    carry three digits into an exponential).  One warp per (token, 8 rows).
-// mlstm_gate_scan:   per (sequence, head), from the gates' pre-activations pre[t] = (i~, f~):
+//                    carry three digits into an exponential).  One warp per (token, row).
+// mlstm_gate_scan:   per (sequence, head), from the gates' pre-activations pre[t] = (i~, f~) (+ a bias [2 heads]):
 //                      log_i = cap tanh(i~ / cap),  log_f = logsigmoid(cap tanh(f~ / cap))
 //                      m_t = max(log_f + m_(t-1), log_i)        m before a request's first token is 0
 //                      decay_t = exp(log_f + m_(t-1) - m_t),  kscale_t = exp(log_i - m_t)
@@ -29,53 +29,44 @@ __device__ __forceinline__ float rg_log_sigmoid(float z) { return fminf(z, 0.f) 
 __device__ __forceinline__ float rg_softplus(float z) { return fmaxf(z, 0.f) + log1pf(expf(-fabsf(z))); }
 __device__ __forceinline__ float rg_silu(float z) { return z / (1.f + expf(-z)); }
 
-#define RD_ROWS 8  // weight rows a warp carries per pass over its token's row
-
 template <typename TA>
 __global__ void rows_dot_f32_kernel(const TA* __restrict__ x, long long ld_x, const float* __restrict__ w, const float* __restrict__ bias,
                                     float* __restrict__ out, int T, int R, int W) {
   ts_pdl_prologue();
-  // One warp per (token, block of RD_ROWS weight rows): every entry of the token's row is read once per block and meets
-  // RD_ROWS weights; the warps of a CTA take consecutive tokens of the same block, so the weights stay in L1.
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int r0 = blockIdx.y * RD_ROWS;
-  if (t >= T) return;
+  if (item >= (long long)T * R) return;
+  const int t = (int)(item / R), r = (int)(item - (long long)t * R);
   const TA* xr = x + (size_t)t * ld_x;
-  const float* wr[RD_ROWS];
-#pragma unroll
-  for (int j = 0; j < RD_ROWS; ++j) wr[j] = w + (size_t)min(r0 + j, R - 1) * W;  // (rows beyond the last repeat it and are not stored)
-  float acc[RD_ROWS];
-#pragma unroll
-  for (int j = 0; j < RD_ROWS; ++j) acc[j] = 0.f;
-  for (int i = lane; i < W; i += 32) {
-    const float xv = ts_to_float(xr[i]);
-#pragma unroll
-    for (int j = 0; j < RD_ROWS; ++j) acc[j] = fmaf(xv, wr[j][i], acc[j]);
+  const float* wr = w + (size_t)r * W;
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  int i = lane;
+  for (; i + 96 < W; i += 128) {
+    acc[0] = fmaf(ts_to_float(xr[i]), wr[i], acc[0]);
+    acc[1] = fmaf(ts_to_float(xr[i + 32]), wr[i + 32], acc[1]);
+    acc[2] = fmaf(ts_to_float(xr[i + 64]), wr[i + 64], acc[2]);
+    acc[3] = fmaf(ts_to_float(xr[i + 96]), wr[i + 96], acc[3]);
   }
-#pragma unroll
-  for (int j = 0; j < RD_ROWS; ++j) {
-    const float sum = ts_warp_sum(acc[j]);
-    if (lane == 0 && r0 + j < R) out[(size_t)t * R + r0 + j] = sum + (bias ? bias[r0 + j] : 0.f);
-  }
+  for (; i < W; i += 32) acc[0] = fmaf(ts_to_float(xr[i]), wr[i], acc[0]);
+  const float sum = ts_warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+  if (lane == 0) out[(size_t)t * R + r] = sum + (bias ? bias[r] : 0.f);
 }
 
 TS_EXPORT int ts_rows_dot_f32(const void* x, int act_dtype, long long ld_x, const float* w, const float* bias, float* out, int T, int R, int W,
                               void* stream) {
   if (T <= 0 || R <= 0) return 0;
   if (W <= 0) return TS_ERR_BAD_ARGUMENT;
-  const int row_blocks = (R + RD_ROWS - 1) / RD_ROWS;
-  if (row_blocks > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  const dim3 grid((unsigned)((T + 3) / 4), (unsigned)row_blocks);
+  const long long items = (long long)T * R;
+  const unsigned blocks = (unsigned)((items + 3) / 4);
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    return ts_launch(rows_dot_f32_kernel<float>, grid, dim3(128), 0, s, (const float*)x, ld_x, w, bias, out, T, R, W);
+    return ts_launch(rows_dot_f32_kernel<float>, dim3(blocks), dim3(128), 0, s, (const float*)x, ld_x, w, bias, out, T, R, W);
   if (act_dtype == TS_DTYPE_BF16)
-    return ts_launch(rows_dot_f32_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, (const __nv_bfloat16*)x, ld_x, w, bias, out, T, R, W);
+    return ts_launch(rows_dot_f32_kernel<__nv_bfloat16>, dim3(blocks), dim3(128), 0, s, (const __nv_bfloat16*)x, ld_x, w, bias, out, T, R, W);
   return TS_ERR_BAD_ARGUMENT;
 }
 
-__global__ void mlstm_gate_scan_kernel(const float* __restrict__ pre, float cap, float* __restrict__ m_state, long long slot_stride,
+__global__ void mlstm_gate_scan_kernel(const float* __restrict__ pre, const float* __restrict__ bias, float cap, float* __restrict__ m_state, long long slot_stride,
                                        const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens, float* __restrict__ decay,
                                        float* __restrict__ kscale, float* __restrict__ m_out, int B, int H) {
   ts_pdl_prologue();
@@ -92,8 +83,8 @@ __global__ void mlstm_gate_scan_kernel(const float* __restrict__ pre, float cap,
     const bool valid = t < t_end;
     float log_i = -INFINITY, log_f = 0.f;
     if (valid) {
-      log_i = cap * tanhf(pre[(size_t)t * 2 * H + h] * inv_cap);
-      log_f = rg_log_sigmoid(cap * tanhf(pre[(size_t)t * 2 * H + H + h] * inv_cap));
+      log_i = cap * tanhf((pre[(size_t)t * 2 * H + h] + (bias ? bias[h] : 0.f)) * inv_cap);
+      log_f = rg_log_sigmoid(cap * tanhf((pre[(size_t)t * 2 * H + H + h] + (bias ? bias[H + h] : 0.f)) * inv_cap));
     }
     float a = log_f, bb = log_i;
 #pragma unroll
@@ -117,12 +108,12 @@ __global__ void mlstm_gate_scan_kernel(const float* __restrict__ pre, float cap,
   if (lane == 0) *mp = carry;
 }
 
-TS_EXPORT int ts_mlstm_gate_scan(const float* pre, float cap, float* m_state, long long slot_stride, const int* state_slots,
+TS_EXPORT int ts_mlstm_gate_scan(const float* pre, const float* bias, float cap, float* m_state, long long slot_stride, const int* state_slots,
                                  const int* cu_seqlens, float* decay, float* kscale, float* m_out, int B, int H, void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || !(cap > 0.f)) return TS_ERR_BAD_ARGUMENT;
   const unsigned blocks = (unsigned)(((long long)B * H + 3) / 4);
-  return ts_launch(mlstm_gate_scan_kernel, dim3(blocks), dim3(128), 0, (cudaStream_t)stream, pre, cap, m_state, slot_stride, state_slots,
+  return ts_launch(mlstm_gate_scan_kernel, dim3(blocks), dim3(128), 0, (cudaStream_t)stream, pre, bias, cap, m_state, slot_stride, state_slots,
                    cu_seqlens, decay, kscale, m_out, B, H);
 }
 

@@ -754,7 +754,7 @@ _SIGNATURES.update({
     "ts_linear_scan": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_void_p, _c_float, _c_void_p, _c_ll, _c_void_p,
                        _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p],
     "ts_rows_dot_f32": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_void_p],
-    "ts_mlstm_gate_scan": [_c_void_p, _c_float, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
+    "ts_mlstm_gate_scan": [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
     "ts_mlstm_norm_gate": [_c_void_p, _c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "ts_ssm_conv": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int,
                     _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p],
@@ -848,13 +848,18 @@ def rows_dot_f32(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
 
 
 def mlstm_gate_scan(pre: torch.Tensor, cap: float, m_state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, num_seqs: int,
-                    num_heads: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """From pre [T, 2H] float32 (input-gate rows, then forget-gate rows): the running maximum m of the
+                    num_heads: int, bias: Optional[torch.Tensor] = None) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """From pre [T, 2H] float32 (input-gate rows, then forget-gate rows; `bias` [2H] float32 is added): the running maximum m of the
     gates' logarithms per (token, head), carried in m_state [slots, >= H] (a view whose rows are the
     requests' slots), and what the recurrence needs of it: decay = exp(log_f + m_prev - m) and
     kscale = exp(log_i - m), each [T, H] float32.  Returns (decay, kscale, m)."""
     H = int(num_heads)
+    flush_gemm_chain()
     _cuda_contig("pre", pre, torch.float32)
+    if bias is not None:
+        _cuda_contig("bias", bias, torch.float32)
+        if bias.numel() != 2 * H:
+            raise KernelError(f"mlstm_gate_scan: bias must have {2 * H} entries, got {bias.numel()}")
     T = pre.shape[0]
     if pre.shape != (T, 2 * H):
         raise KernelError(f"mlstm_gate_scan: pre must be [{T}, {2 * H}], got {tuple(pre.shape)}")
@@ -863,7 +868,7 @@ def mlstm_gate_scan(pre: torch.Tensor, cap: float, m_state: torch.Tensor, state_
     decay = torch.empty((T, H), device=pre.device, dtype=torch.float32)
     kscale = torch.empty_like(decay)
     m = torch.empty_like(decay)
-    _check("mlstm_gate_scan", _fn("ts_mlstm_gate_scan")(pre.data_ptr(), float(cap), m_state.data_ptr(), m_state.stride(0), state_slots.data_ptr(),
+    _check("mlstm_gate_scan", _fn("ts_mlstm_gate_scan")(pre.data_ptr(), _ptr(bias), float(cap), m_state.data_ptr(), m_state.stride(0), state_slots.data_ptr(),
                                                         cu_seqlens.data_ptr(), decay.data_ptr(), kscale.data_ptr(), m.data_ptr(),
                                                         int(num_seqs), H, _stream()))
     return decay, kscale, m

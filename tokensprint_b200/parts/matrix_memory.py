@@ -9,7 +9,7 @@ import torch
 
 from tokensprint_b200 import ops
 from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, Mixer, StepContext, TensorSpec, register_part
-from tokensprint_b200.parts.linear import linear
+from tokensprint_b200.parts.linear import linear, linear_float32_out
 
 
 @register_part("mixer", "matrix_memory")
@@ -25,7 +25,8 @@ class MatrixMemory(Mixer):
 
     Parameters: `hidden_size`, `num_heads`, `key_dim`, `value_dim`, `gate_cap`, `norm_eps`, `q_scale`
     (default key_dim^-0.5) and the tensors' names.  q, k, v and the output gate come from one stacked
-    product in the compute dtype; the two gates' pre-activations from float32 rows and sums; gates,
+    product in the compute dtype; the two gates' pre-activations from a product of their own whose
+    sums leave in float32 (never rounded to the compute dtype); their biases, the tanh caps, gates,
     running maximum, memory, normaliser, read-out and head norm are float32 whatever the compute
     dtype.  The state slot holds [heads, d, e + 1] (memory with the normaliser as a last column)
     followed by [heads] running maxima; it is carried from step to step, so prompts may be cut anywhere."""
@@ -47,7 +48,7 @@ class MatrixMemory(Mixer):
                       "f": forget_gate, "f_bias": forget_gate_bias}
         self.memory_floats = self.num_heads * self.key_dim * (self.value_dim + 1)
         self.in_weight: Optional[torch.Tensor] = None  # [q | k | v | gate] stacked
-        self.gates_weight: Optional[torch.Tensor] = None  # [input-gate rows ; forget-gate rows] float32
+        self.gates_weight: Optional[torch.Tensor] = None  # [input-gate rows ; forget-gate rows]
         self.gates_bias: Optional[torch.Tensor] = None
         self.norm_weight: Optional[torch.Tensor] = None
         self.o_weight: Optional[torch.Tensor] = None
@@ -62,8 +63,8 @@ class MatrixMemory(Mixer):
         W, n, H = self.hidden_size, self.names, self.num_heads
         hd, he = H * self.key_dim, H * self.value_dim
         return [TensorSpec(n["q"], (hd, W)), TensorSpec(n["k"], (hd, W)), TensorSpec(n["v"], (he, W)), TensorSpec(n["gate"], (he, W)),
-                TensorSpec(n["o"], (W, he)), TensorSpec(n["norm"], (he,), "vector"), TensorSpec(n["i"], (H, W), "vector"),
-                TensorSpec(n["i_bias"], (H,), "vector"), TensorSpec(n["f"], (H, W), "vector"), TensorSpec(n["f_bias"], (H,), "vector")]
+                TensorSpec(n["o"], (W, he)), TensorSpec(n["norm"], (he,), "vector"), TensorSpec(n["i"], (H, W)),
+                TensorSpec(n["i_bias"], (H,), "vector"), TensorSpec(n["f"], (H, W)), TensorSpec(n["f_bias"], (H,), "vector")]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         n = self.names
@@ -80,10 +81,9 @@ class MatrixMemory(Mixer):
         T, H, d, e = x.shape[0], self.num_heads, self.key_dim, self.value_dim
         hd, he = H * d, H * e
         state = cache.state.view(cache.state.shape[0], -1)
-        pre = torch.empty((T, 2 * H), device=x.device, dtype=torch.float32)
-        ops.rows_dot_f32(x, self.gates_weight, self.gates_bias, pre)
+        pre = linear_float32_out(x, self.gates_weight)
         decay, kscale, m = ops.mlstm_gate_scan(pre, self.gate_cap, state[:, self.memory_floats:], step.state_slots, step.cu_seqlens_q,
-                                               step.num_seqs, H)
+                                               step.num_seqs, H, bias=self.gates_bias)
         proj = linear(x, self.in_weight, next_weight=self.o_weight)
         q, k, v, gate = proj[:, :hd], proj[:, hd:2 * hd], proj[:, 2 * hd:2 * hd + he], proj[:, 2 * hd + he:]
         o = torch.empty((T, H * (e + 1)), device=x.device, dtype=torch.float32)

@@ -9,7 +9,7 @@ import torch
 
 from tokensprint_b200 import ops
 from tokensprint_b200.parts.base import BuildContext, CacheNeed, LayerCache, Mixer, StepContext, TensorSpec, register_part
-from tokensprint_b200.parts.linear import linear
+from tokensprint_b200.parts.linear import linear, linear_float32_out
 
 
 @register_part("mixer", "state_space")
@@ -24,8 +24,8 @@ class StateSpace(Mixer):
         out = W_o ( norm_in_parts(y * silu(z)) * w_norm )       the row in `norm_groups` equal parts, each by its own rms
 
     Parameters: `hidden_size`, `num_heads`, `value_dim`, `state_dim`, `groups`, `taps`, `norm_groups`,
-    `norm_eps` and the tensors' names.  The step-size rows of W_in are applied with float32 weights
-    and sums; the convolution, the step sizes, decays, the state, the recurrence and the norm are
+    `norm_eps` and the tensors' names.  The step-size rows of W_in are a product of their own whose
+    sums leave in float32 (never rounded to the compute dtype); the convolution, the step sizes, decays, the state, the recurrence and the norm are
     float32 whatever the compute dtype.  The state slot holds [H, N, e] followed by the last taps - 1
     inputs of the convolution [taps - 1, inner + 2 G N], oldest first; zeros before the first token."""
 
@@ -49,7 +49,7 @@ class StateSpace(Mixer):
         self.memory_floats = self.num_heads * self.state_dim * self.value_dim
         self.names = {"in": in_proj, "conv": conv, "conv_bias": conv_bias, "dt_bias": dt_bias, "a_log": a_log, "skip": skip, "norm": norm, "o": o}
         self.in_weight: Optional[torch.Tensor] = None  # the rows of z, x, B, C
-        self.dt_weight: Optional[torch.Tensor] = None  # the step-size rows, float32
+        self.dt_weight: Optional[torch.Tensor] = None  # the step-size rows
         self.o_weight: Optional[torch.Tensor] = None
 
     def first_weight(self) -> Optional[torch.Tensor]:
@@ -70,7 +70,7 @@ class StateSpace(Mixer):
         w = tensors[n["in"]]
         rows = self.inner + self.channels
         self.in_weight = w[:rows].contiguous()
-        self.dt_weight = w[rows:].to(torch.float32).contiguous()  # (a stored bfloat16 widens without loss)
+        self.dt_weight = w[rows:].contiguous()
         self.conv_weight, self.conv_bias = tensors[n["conv"]], tensors[n["conv_bias"]]
         self.dt_bias, self.a_log, self.skip = tensors[n["dt_bias"]], tensors[n["a_log"]], tensors[n["skip"]]
         self.norm_weight, self.o_weight = tensors[n["norm"]], tensors[n["o"]]
@@ -83,8 +83,7 @@ class StateSpace(Mixer):
         T, H, e, N, G = x.shape[0], self.num_heads, self.value_dim, self.state_dim, self.groups
         inner, GN = self.inner, self.groups * self.state_dim
         state = cache.state.view(cache.state.shape[0], -1)
-        dt_raw = torch.empty((T, H), device=x.device, dtype=torch.float32)
-        ops.rows_dot_f32(x, self.dt_weight, None, dt_raw)
+        dt_raw = linear_float32_out(x, self.dt_weight)
         proj = linear(x, self.in_weight, next_weight=self.o_weight)
         z = proj[:, :inner]
         conv, dt, decay = ops.ssm_conv(proj[:, inner:], self.conv_weight, self.conv_bias, state[:, self.memory_floats:], step.state_slots,
