@@ -131,7 +131,20 @@ PEK_LONG = {
     ],
 }
 
-PEK = {"a": PEK_A, "b": PEK_B, "c": PEK_C, "d": PEK_D}
+# a width and a vocabulary that are multiples of nothing useful, three heads everywhere; the layers begin with the
+# state-space mixer, and it is the pair side by side whose weights run a second time
+_E1 = _par(_left(2, 1, 12, 10, 0.5, _rot(777.0, 12, _llama(3.0, 0.5, 2.0, 50))), _right(3, 16, 12, 6.0), 0.9, 1.1)
+PEK_E = {
+    "architecture": "Pekunex", "vocab": 97, "width": 100, "norm": {"eps": 2e-5}, "embedding": {"scale": 1.7}, "logit_scale": 1.3,
+    "layers": [
+        _layer(_ssm(3, 9, 6, 3, 3, 3), 52),
+        _layer(_E1, 52),
+        _layer(_att(3, 3, 10, 14, 1.1, _rot(2000.0, 6, _yarn(3.0, 24, 6.0, 0.75)), softcap=12.0), None),
+        _layer(_E1, 52, weights_of=1),
+    ],
+}
+
+PEK = {"a": PEK_A, "b": PEK_B, "c": PEK_C, "d": PEK_D, "e": PEK_E}
 
 
 def _attention_shapes(p: str, m: dict, W: int, biased: bool) -> dict[str, tuple[int, ...]]:

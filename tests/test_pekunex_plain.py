@@ -115,7 +115,7 @@ def test_state_space_equals_the_decayed_sum_and_convolution_keeps_its_last_input
         assert torch.allclose(plain.short_convolution(u[cut:], taps, bias, before=before), whole[cut:], atol=1e-12)
 
 
-@pytest.mark.parametrize("tag", ["a", "b", "c"])
+@pytest.mark.parametrize("tag", ["a", "b", "c", "e"])
 def test_logits_of_a_prefix_do_not_depend_on_what_follows(tag):
     cfg = PEK[tag]
     w = pekunex_weights(cfg, 7)
