@@ -251,6 +251,52 @@ __global__ void __launch_bounds__(GLA_THREADS, GLA_MIN_BLOCKS) gla_scan_kernel(
   }
 }
 
+
+// A step in which every sequence brings one token at most (decode): nothing is staged, no barrier is met.  One CTA per
+// (sequence, head, block of value columns) as above; a thread reads the token's q, k and decay entries of its own
+// channels straight from device memory (the lanes of other columns read the same words), updates its part of the
+// state's column once and adds the read-out over the column's lanes.  Few registers, so many CTAs an SM: a decode
+// step is a chain of a few dependent loads per CTA and nothing else, and only CTAs in flight hide it.
+template <typename TA, int KP>
+__global__ void __launch_bounds__(GLA_THREADS) gla_step_kernel(
+    const TA* __restrict__ q, const TA* __restrict__ k, const TA* __restrict__ v, long long ld_qkv, const float* __restrict__ decay,
+    float q_scale, float* __restrict__ state, const int* __restrict__ state_slots, const int* __restrict__ cu_seqlens,
+    float* __restrict__ o, int H, int d, int e, int R, int cols_per_cta, const float* __restrict__ kscale, int decay_scalar, int groups,
+    int ev, long long slot_stride) {
+  ts_pdl_prologue();
+  const int b = blockIdx.x, h = blockIdx.y, col0 = blockIdx.z * cols_per_cta;
+  const int t = cu_seqlens[b];
+  if (cu_seqlens[b + 1] <= t) return;  // a lane of a fixed-size batch without a request
+  const int r = threadIdx.x % R, cj = threadIdx.x / R;
+  const int col = col0 + cj;
+  const bool has_col = col < e;
+  float* S = state + (size_t)state_slots[b] * slot_stride + ((size_t)h * d) * e;
+  float s_reg[KP];
+#pragma unroll
+  for (int i = 0; i < KP; ++i) s_reg[i] = (has_col && CH(i) < d) ? S[(size_t)(CH(i)) * e + col] : 0.f;
+  const size_t row = (size_t)t * ld_qkv, qk_off = (size_t)(h / (H / groups)) * d;
+  const float scale_k = kscale ? kscale[(size_t)t * H + h] : 1.f;
+  const float a_all = decay_scalar ? decay[(size_t)t * H + h] : 1.f;
+  const float* a_row = decay + (size_t)t * H * d + (size_t)h * d;
+  const float vv = !has_col ? 0.f : (col < ev ? ts_to_float(v[row + (size_t)h * ev + col]) : 1.f);
+  float acc = 0.f;
+#pragma unroll
+  for (int i = 0; i < KP; ++i) {
+    const int ch = CH(i);
+    if (ch < d) {
+      const float a = decay_scalar ? a_all : a_row[ch];
+      s_reg[i] = fmaf(a, s_reg[i], ts_to_float(k[row + qk_off + ch]) * scale_k * vv);
+      acc = fmaf(s_reg[i], ts_to_float(q[row + qk_off + ch]) * q_scale, acc);
+    }
+  }
+  for (int w = 1; w < R; w <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+  if (has_col) {
+    if (r == 0) o[((size_t)t * H + h) * e + col] = acc;
+#pragma unroll
+    for (int i = 0; i < KP; ++i)
+      if (CH(i) < d) S[(size_t)(CH(i)) * e + col] = s_reg[i];
+  }
+}
 #undef CH
 
 // What the general form of the recurrence has beyond gated linear attention's (see ts_linear_scan).
@@ -301,6 +347,26 @@ static int dispatch_gla_scan(const void* q, const void* k, const void* v, long l
   // R lanes per column, a power of two, so that a thread holds at most GLA_MAX_KP channels
   int R = 1;
   while (R < 32 && (d + R - 1) / R > GLA_MAX_KP) R <<= 1;
+  if (segs == 1 && seg_len == 1) {
+    // one token per sequence at most: the kernel without staging, as few lanes per column as the registers allow
+    // (a warp then covers 32 / R consecutive columns of a state row), more while the grid would leave SMs idle
+    while (R < 32 && (d + R - 1) / R > 4 && (long long)B * H * ((e + GLA_THREADS / R - 1) / (GLA_THREADS / R)) < 4 * 148) R <<= 1;
+    const int kp1 = (d + R - 1) / R, cols = GLA_THREADS / R;
+    const dim3 grid(B, H, (e + cols - 1) / cols);
+    if (grid.y > 65535 || grid.z > 65535) return TS_ERR_UNSUPPORTED_SIZE;
+#define GLA_STEP_CASE(KP) \
+    if (kp1 <= KP) \
+      return ts_launch(gla_step_kernel<TA, KP>, grid, dim3(GLA_THREADS), 0, s, (const TA*)q, (const TA*)k, (const TA*)v, ld_qkv, decay, q_scale, \
+                       state, state_slots, cu_seqlens, o, H, d, e, R, cols, x.kscale, x.decay_scalar, x.groups, x.ev, x.slot_stride)
+    GLA_STEP_CASE(4);
+    GLA_STEP_CASE(8);
+    GLA_STEP_CASE(12);
+    GLA_STEP_CASE(16);
+    GLA_STEP_CASE(24);
+    GLA_STEP_CASE(32);
+#undef GLA_STEP_CASE
+    return TS_ERR_UNSUPPORTED_SIZE;
+  }
   // more lanes per column (fewer channels per thread, more CTAs) while the grid would leave SMs idle
   // or a thread's chain of updates per token would be long; a function of the sizes and the batch alone
   while (R < 32 && (d + R - 1) / R > 4 &&
@@ -365,6 +431,8 @@ TS_EXPORT long long ts_gla_scan_scratch_floats(int B, int segs, int H, int d, in
 // result); decay [T, H*d] float32 (gla_decay); state [slots, H, d, e] float32; o [T, H*e] float32.
 // segs > 1: every sequence's tokens of the step are cut into segments of seg_len tokens (segs * seg_len
 // covers the longest) that run side by side, through `scratch` (ts_gla_scan_scratch_floats); two launches.
+// segs == 1: seg_len is the longest portion of the step where the caller knows it, else 0; 1 (every sequence
+// brings one token at most) runs the kernel that stages nothing.
 TS_EXPORT int ts_gla_scan(const void* q, const void* k, const void* v, long long ld_qkv, int act_dtype, const float* decay, float q_scale,
                           float* state, const int* state_slots, const int* cu_seqlens, float* o, int B, int H, int d, int e, int segs,
                           int seg_len, float* scratch, void* stream) {

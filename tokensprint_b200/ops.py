@@ -715,6 +715,8 @@ def gla_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, z: torch.Tensor,
     code, stream = _act_code("q", q), _stream()
     _check("gla_scan", _fn("ts_gla_decay")(z.data_ptr(), z.stride(0), code, _ptr(bias), float(tau), decay.data_ptr(), T, H * d, stream))
     segs, seg_len = gla_segments(int(num_seqs), max_seqlen)
+    if segs == 1 and max_seqlen == 1:
+        seg_len = 1  # every sequence brings one token at most: the kernel that stages nothing
     scratch = None
     if segs > 1:
         need = int(num_seqs) * segs * H * d * e + int(num_seqs) * segs * H * d + int(num_seqs) * H * d * e
@@ -818,6 +820,8 @@ def linear_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.
     if state_slots.numel() < num_seqs or cu_seqlens.numel() < num_seqs + 1:
         raise KernelError("linear_scan: state_slots and cu_seqlens are shorter than the batch")
     segs, seg_len = gla_segments(int(num_seqs), max_seqlen)
+    if segs == 1 and max_seqlen == 1:
+        seg_len = 1  # every sequence brings one token at most: the kernel that stages nothing
     scratch = None
     if segs > 1:
         need = int(num_seqs) * segs * H * d * ee + int(num_seqs) * segs * H * d + int(num_seqs) * H * d * ee
