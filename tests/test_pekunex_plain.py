@@ -218,3 +218,14 @@ def test_cache_needs_of_the_mixers():
     assert needs[0].k_row == (2, 24) and needs[0].state_shape is None
     assert needs[1].k_row == (1, 20) and needs[1].state_shape == (3 * 12 * 21 + 3,)
     assert needs[2].state_shape == (4 * 8 * 12 + 2 * (48 + 2 * 16),)
+
+
+def test_long_portions_run_in_segments_only_while_the_grid_is_small():
+    from tokensprint_b200 import ops
+
+    few = ops.gla_ctas_per_sequence(4, 32, 49)      # 4 heads, a block of 64 columns each
+    many = ops.gla_ctas_per_sequence(128, 128, 64)  # 128 heads, four blocks of 16 columns each
+    assert few == 4 and many == 512
+    assert ops.gla_segments(1, 1200, few) == (5, 256) and ops.gla_segments(1, 300, few) == (1, 0)
+    assert ops.gla_segments(1, 1200, many) == (1, 0) and ops.gla_segments(80, 1200, few) == (1, 0)
+    assert ops.gla_segments(1, 1200) == (5, 256) and ops.gla_segments(1, None, few) == (1, 0)

@@ -29,7 +29,8 @@
 #define GLA_PF 8         // staged q (k, z) entries a thread fetches ahead per round: tb * dp <= GLA_THREADS * GLA_PF
 #define GLA_PFV 4        // likewise for v: tb * cols <= GLA_THREADS * GLA_PFV
 #ifndef GLA_MIN_BLOCKS
-#define GLA_MIN_BLOCKS 1 // CTAs per SM the compiler plans the registers for
+#define GLA_MIN_BLOCKS 4 // CTAs per SM the compiler plans the registers for (the scan waits on its own chain of updates: only more
+                         // warps hide it; measured 1 / 3 / 4: 1.26 / 1.14 / 1.19 ms in segments, 1.56 / 1.58 / 1.25 in one piece)
 #endif
 #ifndef GLA_UNROLL
 #define GLA_UNROLL 4     // tokens of a round whose loads and shuffles are in flight together
