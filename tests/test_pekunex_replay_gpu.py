@@ -219,3 +219,38 @@ def test_greedy_generation_through_the_entry_point(models, tag, eager, overlap):
     cm = engine.model_runner.cache_manager
     cm.check_invariants()
     assert all(cm.pages_in_use(g) == 0 for g in range(len(cm.pools)))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_the_trace_runner_as_a_program(models, tmp_path, dtype):
+    """bin/trace_run over stdin and stdout with a Pekunex folder: two requests, a portion of one beside single
+    tokens of the other, a step in which nothing is wanted, files in --out, `done <step>` after every step."""
+    import json
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import numpy as np
+
+    folder, cfg, requests, oracle = models["a", dtype]
+    p, q = requests["r4"], requests["r2"]
+    steps = [
+        {"step": 0, "entries": [{"id": "p", "tokens": p[:40], "want": [0, 39]}], "end": []},
+        {"step": 1, "entries": [{"id": "q", "tokens": q[:15], "want": [14]}, {"id": "p", "tokens": p[40:41], "want": [0]}], "end": []},
+        {"step": 2, "entries": [{"id": "p", "tokens": p[41:43], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "q", "tokens": q[15:], "want": [1]}, {"id": "p", "tokens": p[43:], "want": [len(p) - 44]}], "end": ["p", "q"]},
+    ]
+    root = Path(__file__).resolve().parents[1]
+    out = tmp_path / "out"
+    proc = subprocess.run(
+        [sys.executable, str(root / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out), "--max-tokens", "192"],
+        input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [l for l in proc.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    assert sorted(f.name for f in out.iterdir()) == ["0.f32", "1.f32", "3.f32"]
+    want_p, want_q = oracle.logits(p).numpy(), oracle.logits(q).numpy()
+    got = {n: np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, cfg["vocab"]) for n in (0, 1, 3)}
+    pairs = [(got[0][0], want_p[0]), (got[0][1], want_p[39]), (got[1][0], want_q[14]), (got[1][1], want_p[40]),
+             (got[3][0], want_q[16]), (got[3][1], want_p[-1])]
+    for g, w in pairs:
+        assert np.abs(g - w).max() < TOLERANCE[dtype] * max(np.abs(want_p).max(), np.abs(want_q).max())
