@@ -9,7 +9,9 @@
 // the keys; o = sum p * v.  With `has_sink` the softmax's denominator also holds exp(sink_score):
 // a key that every query sees, whose score is fixed and which has no value; with `head_sinks` that
 // score is a number per query head, read from device memory.  With `softcap` > 0 the scaled score
-// passes through softcap * tanh(s / softcap) before the softmax.  Scores, running
+// passes through softcap * tanh(s / softcap) before the softmax.  With `dist_r1` and `dist_r2` (a number
+// per query head each) the score of key j then loses r1 * ln(1 + r2 * (p - j)): a penalty that grows
+// with the logarithm of the distance.  Scores, running
 // max and sum, and the output accumulate in float32
 // (engine/nn/sdpa.py:56,85-102 of the reference: scale head_dim^-0.5, causal, GQA by head
 // ratio, keys and values read through the block table).  Key j of sequence b lives at
@@ -29,7 +31,8 @@ __global__ void attention_paged_simple_kernel(
     const TA* __restrict__ q, const TA* __restrict__ kcache, const TA* __restrict__ vcache,
     TA* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ seq_index,
     const int* __restrict__ block_table, int max_blocks, int page, int T, int nq, int nkv, int d,
-    float scale, int window, int chunk, int has_sink, float sink_score, float softcap, const float* __restrict__ head_sinks) {
+    float scale, int window, int chunk, int has_sink, float sink_score, float softcap, const float* __restrict__ head_sinks,
+    const float* __restrict__ dist_r1, const float* __restrict__ dist_r2) {
   ts_pdl_prologue();
   __shared__ float qs[ATS_WARPS][ATS_MAX_HEAD_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -48,6 +51,7 @@ __global__ void attention_paged_simple_kernel(
   int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   if (chunk > 0) lo = max(lo, p / chunk * chunk);
   const int* table = block_table + (size_t)b * max_blocks;
+  const float r1 = dist_r1 ? dist_r1[g] : 0.f, r2 = dist_r1 ? dist_r2[g] : 0.f;
 
   const TA* qrow = q + ((size_t)t * nq + g) * d;
   for (int i = lane; i < d; i += 32) qs[warp][i] = ts_to_float(qrow[i]) * scale;
@@ -69,6 +73,7 @@ __global__ void attention_paged_simple_kernel(
       float dot = 0.f;
       for (int i = 0; i < d; ++i) dot += qs[warp][i] * ts_to_float(krow[i]);
       s = softcap > 0.f ? softcap * tanhf(dot / softcap) : dot;
+      if (dist_r1) s -= r1 * log1pf(r2 * (float)(p - j));
     }
     const float m_new = fmaxf(m, ts_warp_max(s));
     const float corr = expf(m - m_new);  // m = -inf on the first round: exp(-inf) = 0
@@ -111,10 +116,12 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
                                         const int* seq_index, const int* block_table,
                                         int max_blocks, int page, int T, int nq, int nkv, int d,
                                         float scale, int window, int chunk, int has_sink, float sink_score,
-                                        float softcap, const float* head_sinks, void* stream) {
+                                        float softcap, const float* head_sinks, const float* dist_r1, const float* dist_r2,
+                                        void* stream) {
   if (T <= 0) return 0;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || d <= 0 || page <= 0 || max_blocks <= 0)
     return TS_ERR_BAD_ARGUMENT;
+  if ((dist_r1 == nullptr) != (dist_r2 == nullptr)) return TS_ERR_BAD_ARGUMENT;
   if (d > ATS_MAX_HEAD_DIM) return TS_ERR_UNSUPPORTED_SIZE;
   long long items = (long long)T * nq;
   unsigned blocks = (unsigned)((items + ATS_WARPS - 1) / ATS_WARPS);
@@ -122,12 +129,12 @@ TS_EXPORT int ts_attention_paged_simple(const void* q, const void* kcache, const
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(attention_paged_simple_kernel<float>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const float*)q, (const float*)kcache, (const float*)vcache, (float*)out, positions,
-        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window, chunk, has_sink, sink_score, softcap, head_sinks);
+        seq_index, block_table, max_blocks, page, T, nq, nkv, d, scale, window, chunk, has_sink, sink_score, softcap, head_sinks, dist_r1, dist_r2);
   else if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(attention_paged_simple_kernel<__nv_bfloat16>, dim3(blocks), dim3(ATS_WARPS * 32), 0, s,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
         (__nv_bfloat16*)out, positions, seq_index, block_table, max_blocks, page, T, nq, nkv, d,
-        scale, window, chunk, has_sink, sink_score, softcap, head_sinks);
+        scale, window, chunk, has_sink, sink_score, softcap, head_sinks, dist_r1, dist_r2);
   else
     return TS_ERR_BAD_ARGUMENT;
   return ts_launch_status();

@@ -11,7 +11,10 @@
 //   latent_prepare: per token, from the stacked projection [q heads | latent and key part | gate
 //     logits]: RMS norm of the latent, rotation of the key part and of every head's rotated
 //     query part (angles, sines and cosines in float32), store of [c ; r] into the cache by slot,
-//     rotated query parts into the absorbed-query buffer, sigmoid of the gate logits.
+//     rotated query parts into the absorbed-query buffer, sigmoid of the gate logits.  Cosines and
+//     sines may carry a `magnitude` (stretched frequencies come with one).  The queries may come
+//     from a tensor of their own (`q_src`: a layer whose queries pass a latent first), and a layer
+//     that reads another layer's cached rows has no latent of its own (`kv_off` < 0: queries only).
 //   latent_attention_simple: CUDA cores, one warp per (token, head), scores, softmax and sums in
 //     float32: the float32 path's attention and the yardstick of the tensor-core kernel.
 #include "common.cuh"
@@ -48,7 +51,7 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
                                       TA* __restrict__ q_abs, TA* __restrict__ cache, const int* __restrict__ slot_mapping,
                                       const int* __restrict__ positions, const float* __restrict__ latent_weight, float eps,
                                       const float* __restrict__ inv_freq, int rot_dims, int pairing, float* __restrict__ gates,
-                                      int H, int nope, int rot, int rank) {
+                                      int H, int nope, int rot, int rank, float magnitude, const TA* __restrict__ q_src, long long ld_q) {
   ts_pdl_prologue();
   __shared__ float scratch[33];
   __shared__ float2 cs[LAT_MAX_PAIRS];  // (cos, sin) of the token's angles, shared by the key part and every head
@@ -58,17 +61,18 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
   for (int i = threadIdx.x; i < (rot_dims >> 1); i += blockDim.x) {
     float sn, c;
     sincosf(pos * inv_freq[i], &sn, &c);
-    cs[i] = make_float2(c, sn);
+    cs[i] = make_float2(c * magnitude, sn * magnitude);
   }  // the block-wide sum below has a barrier before anyone reads the table
-  const int slot = slot_mapping ? slot_mapping[t] : -1;
+  const int slot = (slot_mapping && kv_off >= 0) ? slot_mapping[t] : -1;
   const int key_dim = rank + rot;
   // the latent: RMS norm with a plain weight
-  const TA* lat = row + kv_off;
+  const TA* lat = row + (kv_off >= 0 ? kv_off : 0);
   float ss = 0.f;
-  for (int i = threadIdx.x; i < rank; i += blockDim.x) {
-    const float v = ts_to_float(lat[i]);
-    ss += v * v;
-  }
+  if (kv_off >= 0)
+    for (int i = threadIdx.x; i < rank; i += blockDim.x) {
+      const float v = ts_to_float(lat[i]);
+      ss += v * v;
+    }
   ss = ts_block_sum(ss, scratch);
   const float rstd = 1.f / sqrtf(ss / (float)rank + eps);
   if (slot >= 0) {
@@ -80,7 +84,7 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
   // every head's rotated query part, behind the place of its absorbed part
   for (int i = threadIdx.x; i < H * rot; i += blockDim.x) {
     const int a = i / rot, j = i - a * rot;
-    const TA* qr = row + q_off + (size_t)a * (nope + rot) + nope;
+    const TA* qr = (q_src ? q_src + (size_t)t * ld_q : row + q_off) + (size_t)a * (nope + rot) + nope;
     q_abs[((size_t)t * H + a) * key_dim + rank + j] = ts_from_float<TA>(lat_rotated(qr, j, rot_dims, pairing, cs));
   }
   if (gates)
@@ -90,22 +94,22 @@ __global__ void latent_prepare_kernel(const TA* __restrict__ proj, long long ld,
 TS_EXPORT int ts_latent_prepare(const void* proj, int act_dtype, long long ld, int q_off, int kv_off, int gate_off, void* q_abs,
                                 void* cache, const int* slot_mapping, const int* positions, const float* latent_weight, float eps,
                                 const float* inv_freq, int rot_dims, int pairing, float* gates, int T, int H, int nope, int rot,
-                                int rank, void* stream) {
+                                int rank, float magnitude, const void* q_src, long long ld_q, void* stream) {
   if (T <= 0) return 0;
   if (rot_dims > 2 * LAT_MAX_PAIRS) return TS_ERR_UNSUPPORTED_SIZE;
   if (H <= 0 || nope < 0 || rot < 0 || rank <= 0 || rot_dims < 0 || rot_dims > rot || (rot_dims & 1) || (rot_dims > 0 && !inv_freq) ||
-      (pairing != LAT_PAIR_HALF && pairing != LAT_PAIR_NEIGHBOURS))
+      (pairing != LAT_PAIR_HALF && pairing != LAT_PAIR_NEIGHBOURS) || (kv_off < 0 && cache != nullptr) || (proj == nullptr && (q_src == nullptr || kv_off >= 0 || gates)))
     return TS_ERR_BAD_ARGUMENT;
   cudaStream_t s = (cudaStream_t)stream;
   const int threads = 128;
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(latent_prepare_kernel<float>, dim3(T), dim3(threads), 0, s, (const float*)proj, ld, q_off, kv_off, gate_off,
                      (float*)q_abs, (float*)cache, slot_mapping, positions, latent_weight, eps, inv_freq, rot_dims, pairing, gates, H,
-                     nope, rot, rank);
+                     nope, rot, rank, magnitude, (const float*)q_src, ld_q);
   if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(latent_prepare_kernel<__nv_bfloat16>, dim3(T), dim3(threads), 0, s, (const __nv_bfloat16*)proj, ld, q_off, kv_off,
                      gate_off, (__nv_bfloat16*)q_abs, (__nv_bfloat16*)cache, slot_mapping, positions, latent_weight, eps, inv_freq,
-                     rot_dims, pairing, gates, H, nope, rot, rank);
+                     rot_dims, pairing, gates, H, nope, rot, rank, magnitude, (const __nv_bfloat16*)q_src, ld_q);
   return TS_ERR_BAD_ARGUMENT;
 }
 

@@ -4,7 +4,9 @@
 //   router_topk : per token, from float32 router logits (+ a bias per expert, if given): the `top`
 //                 largest logits (the lower index wins a tie) with their experts; their weights are
 //                 sigmoid(logit), handed on as they are or divided by their sum (`renormalize`), or
-//                 the softmax over the chosen logits alone (`score_mode`).
+//                 the softmax over the chosen logits alone (`score_mode`); or, with the softmax over all
+//                 logits as scores, the `top` largest of score + correction (a number per expert that
+//                 steers the choice only) with the scores themselves as weights.
 //   moe_plan    : the (token, choice) pairs sorted by expert: offsets[e] .. offsets[e+1] are expert
 //                 e's places in `order` (pair indices), tile_offsets[e] its first row tile of
 //                 `tile_rows` places (64 for the kernels here, more for the tensor-core ones).
@@ -13,8 +15,11 @@
 //                 b = clamp(u, -limit, limit), a * sigmoid(alpha a) * (b + 1); or silu(g) * u
 //                                                                  -> act[place, I]
 //   moe_down    : act[place] times the expert's down matrix       -> pair_out[pair, N]
+//                 Experts without a gate matrix (`act_mode` gelu, gate null): gelu(u) alone.
 //   moe_combine : out[t] = sum over the token's pairs (each times its weight, if weights are given)
-//                 (+ shared[t]), summed in float32 in the order of the choices.
+//                 (+ shared[t]), summed in float32 in the order of the choices.  A chosen index at or
+//                 beyond `E` (given with `ids`) is an identity expert: it has no matrices and no place
+//                 in the plan, and its output is the token's input row x[t] itself.
 //
 // The two products are FFMA tiles of 64 x 64 with float32 sums over k in increasing order: a
 // pair's result does not depend on its place inside its expert's rows, so the order in which the
@@ -29,8 +34,18 @@
 
 
 // The choice of one token by one warp: logits z [E] (shared or global memory), the bias already in.
-__device__ __forceinline__ void router_choose(const float* z, int E, int top, int renormalize, int score_mode, int* my_ids, float* my_w,
-                                              int lane) {
+__device__ __forceinline__ void router_choose(float* z, int E, int top, int renormalize, int score_mode, int* my_ids, float* my_w,
+                                              int lane, const float* __restrict__ correction) {
+  if (score_mode == ROUTER_SCORE_SOFTMAX_ALL) {
+    // z becomes the softmax over all experts; the choice below then runs over z + correction
+    float mx = -INFINITY, sum = 0.f;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, z[e]);
+    mx = ts_warp_max(mx);
+    for (int e = lane; e < E; e += 32) sum += expf(z[e] - mx);
+    sum = ts_warp_sum(sum);
+    for (int e = lane; e < E; e += 32) z[e] = expf(z[e] - mx) / sum;
+    __syncwarp();
+  }
   float total = 0.f, first = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
@@ -38,7 +53,7 @@ __device__ __forceinline__ void router_choose(const float* z, int E, int top, in
     for (int e = lane; e < E; e += 32) {
       bool taken = false;
       for (int j = 0; j < k; ++j) taken |= (my_ids[j] == e);
-      const float v = z[e];
+      const float v = z[e] + (correction ? correction[e] : 0.f);
       if (!taken && (v > best || (v == best && e < best_e))) {
         best = v;
         best_e = e;
@@ -54,7 +69,8 @@ __device__ __forceinline__ void router_choose(const float* z, int E, int top, in
       }
     }
     if (k == 0) first = best;  // the largest logit: the softmax's reference point
-    const float score = score_mode == ROUTER_SCORE_SOFTMAX_CHOSEN ? expf(best - first) : 1.f / (1.f + expf(-best));
+    const float score = score_mode == ROUTER_SCORE_SOFTMAX_ALL ? z[best_e < E ? best_e : 0]
+                      : score_mode == ROUTER_SCORE_SOFTMAX_CHOSEN ? expf(best - first) : 1.f / (1.f + expf(-best));
     total += score;
     if (lane == 0) {
       my_ids[k] = best_e < E ? best_e : 0;
@@ -67,7 +83,7 @@ __device__ __forceinline__ void router_choose(const float* z, int E, int top, in
 }
 
 __global__ void router_topk_kernel(const float* __restrict__ logits, const float* __restrict__ bias, int T, int E, int top, int renormalize,
-                                   int score_mode, int* __restrict__ ids, float* __restrict__ weights) {
+                                   int score_mode, int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ correction) {
   ts_pdl_prologue();
   extern __shared__ float zs[];  // [4][E]: a token's logits with the bias added
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -76,16 +92,16 @@ __global__ void router_topk_kernel(const float* __restrict__ logits, const float
   float* z = zs + (size_t)w * E;
   for (int e = lane; e < E; e += 32) z[e] = logits[(size_t)warp * E + e] + (bias ? bias[e] : 0.f);
   __syncwarp();
-  router_choose(z, E, top, renormalize, score_mode, ids + (size_t)warp * top, weights + (size_t)warp * top, lane);
+  router_choose(z, E, top, renormalize, score_mode, ids + (size_t)warp * top, weights + (size_t)warp * top, lane, correction);
 }
 
 TS_EXPORT int ts_router_topk(const float* logits, const float* bias, int T, int E, int top, int renormalize, int score_mode, int* ids,
-                             float* weights, void* stream) {
+                             float* weights, const float* correction, void* stream) {
   if (T <= 0) return 0;
   if (E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
   if ((size_t)4 * E * sizeof(float) > 48 * 1024) return TS_ERR_UNSUPPORTED_SIZE;
   return ts_launch(router_topk_kernel, dim3((T + 3) / 4), dim3(128), (size_t)4 * E * sizeof(float), (cudaStream_t)stream, logits, bias, T, E,
-                   top, renormalize, score_mode, ids, weights);
+                   top, renormalize, score_mode, ids, weights, correction);
 }
 
 // One block: counts per expert, their prefix sums, then every pair takes the next place of its expert.
@@ -173,7 +189,7 @@ __global__ void __launch_bounds__(256) moe_gate_up_kernel(const TA* __restrict__
       const int gk = k0 + c, gn = n0 + r, sr = src_row[r];
       As[c][r] = (sr >= 0 && gk < K) ? ts_to_float(x[(size_t)sr * K + gk]) * src_scale[r] : 0.f;
       const bool w_ok = gn < I && gk < K;
-      Gs[c][r] = w_ok ? ts_to_float(G[(size_t)gn * K + gk]) : 0.f;
+      Gs[c][r] = (w_ok && gate != nullptr) ? ts_to_float(G[(size_t)gn * K + gk]) : 0.f;
       Us[c][r] = w_ok ? ts_to_float(U[(size_t)gn * K + gk]) : 0.f;
     }
     __syncthreads();
@@ -266,7 +282,7 @@ TS_EXPORT int ts_moe_gate_up(const void* x, int act_dtype, const float* pair_wei
                              const int* tile_offsets, const void* gate, const void* up, void* act, int P, int E, int K, int I, int top,
                              float limit, float alpha, int act_mode, void* stream) {
   if (P <= 0) return 0;
-  if (E <= 0 || K <= 0 || I <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (E <= 0 || K <= 0 || I <= 0 || top <= 0 || ((gate == nullptr) != (act_mode == MOE_ACT_GELU))) return TS_ERR_BAD_ARGUMENT;
   const dim3 grid((I + MOE_BN - 1) / MOE_BN, (P + MOE_BM - 1) / MOE_BM + E);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
@@ -297,30 +313,35 @@ TS_EXPORT int ts_moe_down(const void* act, int act_dtype, const int* order, cons
 
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* __restrict__ pair_out, const TA* __restrict__ shared, TA* __restrict__ out,
-                                   const float* __restrict__ pair_weight, int N, int top, size_t total) {
+                                   const float* __restrict__ pair_weight, int N, int top, size_t total, const int* __restrict__ ids, int E,
+                                   const TA* __restrict__ x) {
   ts_pdl_prologue();
   const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total) return;
   const size_t t = idx / N;
   const int n = (int)(idx - t * N);
   float sum = 0.f;
-  for (int k = 0; k < top; ++k) sum += ts_to_float(pair_out[(t * top + k) * N + n]) * (pair_weight ? pair_weight[t * top + k] : 1.f);
+  for (int k = 0; k < top; ++k) {
+    const bool identity = ids != nullptr && ids[t * top + k] >= E;  // no expert ran for this pair: its output is the input row
+    const float v = identity ? ts_to_float(x[idx]) : ts_to_float(pair_out[(t * top + k) * N + n]);
+    sum += v * (pair_weight ? pair_weight[t * top + k] : 1.f);
+  }
   if (shared) sum += ts_to_float(shared[idx]);
   out[idx] = ts_from_float<TA>(sum);
 }
 
 TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out, const float* pair_weight, int act_dtype, int T, int N,
-                             int top, void* stream) {
+                             int top, const int* ids, int E, const void* x, void* stream) {
   if (T <= 0) return 0;
-  if (N <= 0 || top <= 0) return TS_ERR_BAD_ARGUMENT;
+  if (N <= 0 || top <= 0 || (ids != nullptr && x == nullptr)) return TS_ERR_BAD_ARGUMENT;
   const size_t total = (size_t)T * N;
   const unsigned blocks = (unsigned)((total + 255) / 256);
   cudaStream_t s = (cudaStream_t)stream;
   if (act_dtype == TS_DTYPE_F32)
-    return ts_launch(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)pair_out, (const float*)shared, (float*)out, pair_weight, N, top, total);
+    return ts_launch(moe_combine_kernel<float>, dim3(blocks), dim3(256), 0, s, (const float*)pair_out, (const float*)shared, (float*)out, pair_weight, N, top, total, ids, E, (const float*)x);
   if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(moe_combine_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, s, (const __nv_bfloat16*)pair_out,
-                     (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, pair_weight, N, top, total);
+                     (const __nv_bfloat16*)shared, (__nv_bfloat16*)out, pair_weight, N, top, total, ids, E, (const __nv_bfloat16*)x);
   return TS_ERR_BAD_ARGUMENT;
 }
 
@@ -336,7 +357,8 @@ TS_EXPORT int ts_moe_combine(const void* pair_out, const void* shared, void* out
 template <typename TX>
 __global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, const float* __restrict__ router,
                                                      const float* __restrict__ bias, int T, int W, int E, int top, int renormalize,
-                                                     int score_mode, int rt, int* __restrict__ ids, float* __restrict__ weights) {
+                                                     int score_mode, int rt, int* __restrict__ ids, float* __restrict__ weights,
+                                                     const float* __restrict__ correction) {
   ts_pdl_prologue();
   extern __shared__ float rs[];
   float* xs = rs;                    // [rt][W]
@@ -381,11 +403,11 @@ __global__ void __launch_bounds__(256) router_kernel(const TX* __restrict__ x, c
   __syncthreads();
   if (warp >= nt) return;
   router_choose(logits + (size_t)warp * E, E, top, renormalize, score_mode, ids + (size_t)(t0 + warp) * top,
-                weights + (size_t)(t0 + warp) * top, lane);
+                weights + (size_t)(t0 + warp) * top, lane, correction);
 }
 
 TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, const float* bias, int T, int W, int E, int top, int renormalize,
-                        int score_mode, int* ids, float* weights, void* stream) {
+                        int score_mode, int* ids, float* weights, const float* correction, void* stream) {
   if (T <= 0) return 0;
   if (W <= 0 || E <= 0 || top <= 0 || top > E) return TS_ERR_BAD_ARGUMENT;
   // tokens per CTA: four where there are CTAs enough for every SM several times over (a router row is
@@ -403,7 +425,7 @@ TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, const f
       if (e != cudaSuccess) return (int)e;
       set32 = 227 * 1024;
     }
-    return ts_launch(router_kernel<float>, grid, dim3(256), smem, s, (const float*)x, router, bias, T, W, E, top, renormalize, score_mode, rt, ids, weights);
+    return ts_launch(router_kernel<float>, grid, dim3(256), smem, s, (const float*)x, router, bias, T, W, E, top, renormalize, score_mode, rt, ids, weights, correction);
   }
   if (x_dtype == TS_DTYPE_BF16) {
     static size_t set16 = 0;
@@ -413,7 +435,7 @@ TS_EXPORT int ts_router(const void* x, int x_dtype, const float* router, const f
       set16 = 227 * 1024;
     }
     return ts_launch(router_kernel<__nv_bfloat16>, grid, dim3(256), smem, s, (const __nv_bfloat16*)x, router, bias, T, W, E, top, renormalize,
-                     score_mode, rt, ids, weights);
+                     score_mode, rt, ids, weights, correction);
   }
   return TS_ERR_BAD_ARGUMENT;
 }

@@ -42,14 +42,17 @@ __device__ __forceinline__ int tile_expert(const int* __restrict__ tile_offsets,
 
 // WM x WN warps: a warp owns MT tiles of 16 rows and NB / WN of the 128 weight rows in shared memory
 // (the more of both, the fewer shared-memory loads per MMA: MT + NT / 2 loads feed MT * NT MMAs).
-// GATE_UP: the first half of a warp's weight rows are gate rows and the second half the up rows of
-// the same outputs (so both operands of an activation sit in one thread); else 128 rows of one matrix.
-template <bool GATE_UP, int WM, int WN, int MT, int STAGES>
+// MODE 1 (gate and up): the first half of a warp's weight rows are gate rows and the second half the up
+// rows of the same outputs (so both operands of an activation sit in one thread); else 128 rows of one
+// matrix: MODE 0 the down product (rows of A by place, results by pair), MODE 2 the first product of
+// experts without a gate (rows of A by the pair's token, the activation of the weighted sums by place).
+template <int MODE, int WM, int WN, int MT, int STAGES>
 __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat16* __restrict__ A, const float* __restrict__ pair_weight,
                                                                const int* __restrict__ order, const int* __restrict__ offsets,
                                                                const int* __restrict__ tile_offsets, const __nv_bfloat16* __restrict__ B0,
                                                                const __nv_bfloat16* __restrict__ B1, __nv_bfloat16* __restrict__ out, int E,
                                                                int K, int NOUT, int top, float limit, float alpha, int act_mode) {
+  constexpr bool GATE_UP = MODE == 1, BY_TOKEN = MODE != 0;
   constexpr int BM = 16 * MT * WM, THREADS = 32 * WM * WN, CW = NB / WN, HALF = CW / 2, NT = CW / 8;
   constexpr size_t STAGE_ELEMS = (size_t)(BM + NB) * KS;
   ts_pdl_prologue();
@@ -66,7 +69,7 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
     const int place = row0 + r;
     const int pair = place < row_end ? order[place] : -1;
     a_pair[r] = pair;
-    a_src[r] = pair < 0 ? nullptr : (GATE_UP ? A + (size_t)(pair / top) * K : A + (size_t)place * K);
+    a_src[r] = pair < 0 ? nullptr : (BY_TOKEN ? A + (size_t)(pair / top) * K : A + (size_t)place * K);
   }
   __syncthreads();
   const __nv_bfloat16* W0 = B0 + (size_t)e * NOUT * K;
@@ -167,6 +170,23 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
             if (n + 1 < NOUT) dst[n + 1] = __float2bfloat16_rn(y[1]);
           }
         }
+      } else if (MODE == 2) {
+        const float w = pair_weight[pair];
+        __nv_bfloat16* dst = out + (size_t)(row0 + rl) * NOUT;
+#pragma unroll
+        for (int nb = 0; nb < NT; ++nb) {
+          const int n = n0 + wn * CW + nb * 8 + 2 * qi;
+          float y[2];
+#pragma unroll
+          for (int c = 0; c < 2; ++c)  // the sums are rounded to bfloat16 first, as a product stored to memory would be
+            y[c] = moe_gated_activation(act_mode, 0.f, __bfloat162float(__float2bfloat16_rn(w * acc[m][nb][2 * r + c])), limit, alpha);
+          if (n + 1 < NOUT && (NOUT & 1) == 0) {
+            *reinterpret_cast<__nv_bfloat162*>(dst + n) = __floats2bfloat162_rn(y[0], y[1]);
+          } else {
+            if (n < NOUT) dst[n] = __float2bfloat16_rn(y[0]);
+            if (n + 1 < NOUT) dst[n + 1] = __float2bfloat16_rn(y[1]);
+          }
+        }
       } else {
         __nv_bfloat16* dst = out + (size_t)pair * NOUT;
 #pragma unroll
@@ -188,21 +208,21 @@ __global__ void __launch_bounds__(32 * WM * WN) moe_mma_kernel(const __nv_bfloat
 // flight, three CTAs per SM: the step then streams the chosen experts' weights and little else).
 constexpr int ROWS_MANY = 128, ROWS_FEW = 16;
 
-template <bool GATE_UP, int WM, int WN, int MT, int STAGES>
+template <int MODE, int WM, int WN, int MT, int STAGES>
 int launch(const void* A, const float* pair_weight, const int* order, const int* offsets, const int* tile_offsets, const void* B0,
            const void* B1, void* out, int P, int E, int K, int NOUT, int top, float limit, float alpha, int act_mode, cudaStream_t s) {
   constexpr int BM = 16 * MT * WM;
   constexpr size_t SMEM_BYTES = (size_t)STAGES * (BM + NB) * KS * 2;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<GATE_UP, WM, WN, MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(moe_mma_kernel<MODE, WM, WN, MT, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  const int cols = GATE_UP ? NB / 2 : NB;
+  const int cols = MODE == 1 ? NB / 2 : NB;
   const dim3 grid((NOUT + cols - 1) / cols, (P + BM - 1) / BM + E);
   if (grid.y > 65535) return TS_ERR_UNSUPPORTED_SIZE;
-  return ts_launch(moe_mma_kernel<GATE_UP, WM, WN, MT, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
+  return ts_launch(moe_mma_kernel<MODE, WM, WN, MT, STAGES>, grid, dim3(32 * WM * WN), SMEM_BYTES, s, (const __nv_bfloat16*)A, pair_weight,
                    order, offsets, tile_offsets, (const __nv_bfloat16*)B0, (const __nv_bfloat16*)B1, (__nv_bfloat16*)out, E, K, NOUT, top,
                    limit, alpha, act_mode);
 }
@@ -219,10 +239,16 @@ TS_EXPORT int ts_moe_gate_up_mma(const void* x, const float* pair_weight, const 
                                  int act_mode, int tile_rows, void* stream) {
   if (P <= 0) return 0;
   if (E <= 0 || K <= 0 || I <= 0 || top <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
+  if ((gate == nullptr) != (act_mode == MOE_ACT_GELU)) return TS_ERR_BAD_ARGUMENT;
   if (K % 8 || (((uintptr_t)x | (uintptr_t)gate | (uintptr_t)up) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
+  if (gate == nullptr) {  // experts without a gate matrix: 128 rows of the up matrix per CTA
+    if (tile_rows == ROWS_MANY)
+      return launch<2, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, up, nullptr, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
+    return launch<2, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, up, nullptr, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
+  }
   if (tile_rows == ROWS_MANY)
-    return launch<true, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
-  return launch<true, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
+    return launch<1, 2, 4, 4, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
+  return launch<1, 1, 4, 1, 3>(x, pair_weight, order, offsets, tile_offsets, gate, up, act, P, E, K, I, top, limit, alpha, act_mode, (cudaStream_t)stream);
 }
 
 TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offsets, const int* tile_offsets, const void* down,
@@ -231,6 +257,6 @@ TS_EXPORT int ts_moe_down_mma(const void* act, const int* order, const int* offs
   if (E <= 0 || I <= 0 || N <= 0 || (tile_rows != ROWS_MANY && tile_rows != ROWS_FEW)) return TS_ERR_BAD_ARGUMENT;
   if (I % 8 || (((uintptr_t)act | (uintptr_t)down) & 15)) return TS_ERR_UNSUPPORTED_SIZE;
   if (tile_rows == ROWS_MANY)
-    return launch<false, 2, 4, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
-  return launch<false, 1, 4, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
+    return launch<0, 2, 4, 4, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
+  return launch<0, 1, 4, 1, 3>(act, nullptr, order, offsets, tile_offsets, down, nullptr, pair_out, P, E, I, N, 1, 0.f, 0.f, 0, (cudaStream_t)stream);
 }

@@ -7,7 +7,10 @@
 //               formed and reduced in float64 (inv_freq arrives in float64), the result is float32.
 // qkv_prepare:  one warp per (token, head).  For a query head: x = proj + bias, pair (i, i + rot/2)
 //               of the first `rot` entries turns by the table's angle j = i, the rest stays; with
-//               `unit_norm` the head is then divided by sqrt(mean(x^2) + eps) over its d entries;
+//               `unit_norm` the head is then divided by sqrt(mean(x^2) + eps) over its d entries; with a
+//               query temperature (`qt_every` > 0) a query head is multiplied by
+//               1 + qt_coef * ln(floor((position + 1) / qt_every) + 1): queries grow with the logarithm of
+//               the position, in steps of `qt_every` positions;
 //               written to q_out [T, nq, D], entries d..D-1 zero.  For a key head the same, stored
 //               at the token's cache slot in k_dst [slots, nkv, D]; the value head of the same index
 //               (e entries, bias, nothing else) goes to v_dst [slots, nkv, D], entries e..D-1 zero.
@@ -45,7 +48,7 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
     const TA* __restrict__ proj, long long ld, int q_off, int k_off, int v_off, const float* __restrict__ q_bias,
     const float* __restrict__ k_bias, const float* __restrict__ v_bias, const float2* __restrict__ table, int rot, int unit_norm, float eps,
     TA* __restrict__ q_out, TA* __restrict__ k_dst, TA* __restrict__ v_dst, const int* __restrict__ slot_mapping, int T, int nq, int nkv,
-    int d, int e, int D) {
+    int d, int e, int D, const int* __restrict__ positions, float qt_coef, int qt_every) {
   ts_pdl_prologue();
   __shared__ float buf[QP_WARPS][QP_MAX_DIM];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -82,6 +85,7 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
   __syncwarp();
   float mul = 1.f;
   if (unit_norm) mul = 1.f / sqrtf(ts_warp_sum(ss) / (float)d + eps);
+  if (is_q && qt_every > 0) mul *= 1.f + qt_coef * logf((float)((positions[t] + 1) / qt_every) + 1.f);
   TA* dst = is_q ? q_out + ((size_t)t * nq + h) * D : k_dst + ((size_t)slot * nkv + h) * D;
   for (int i = lane; i < D; i += 32) dst[i] = ts_from_float<TA>(i < d ? x[i] * mul : 0.f);
   if (!is_q && v_dst != nullptr) {
@@ -94,9 +98,11 @@ __global__ void __launch_bounds__(QP_WARPS * 32) qkv_prepare_kernel(
 
 TS_EXPORT int ts_qkv_prepare(const void* proj, int act_dtype, long long ld, int q_off, int k_off, int v_off, const float* q_bias,
                              const float* k_bias, const float* v_bias, const float* table, int rot, int unit_norm, float eps, void* q_out,
-                             void* k_dst, void* v_dst, const int* slot_mapping, int T, int nq, int nkv, int d, int e, int D, void* stream) {
+                             void* k_dst, void* v_dst, const int* slot_mapping, int T, int nq, int nkv, int d, int e, int D, const int* positions,
+                             float qt_coef, int qt_every, void* stream) {
   if (T <= 0) return 0;
-  if (nq < 0 || nkv < 0 || nq + nkv <= 0 || d <= 0 || e <= 0 || D < d || D < e || rot < 0 || rot > d || (rot & 1) || (rot > 0 && table == nullptr))
+  if (nq < 0 || nkv < 0 || nq + nkv <= 0 || d <= 0 || e <= 0 || D < d || D < e || rot < 0 || rot > d || (rot & 1) || (rot > 0 && table == nullptr) ||
+      qt_every < 0 || (qt_every > 0 && positions == nullptr))
     return TS_ERR_BAD_ARGUMENT;
   if (D > QP_MAX_DIM) return TS_ERR_UNSUPPORTED_SIZE;
   const long long items = (long long)T * (nq + nkv);
@@ -105,11 +111,11 @@ TS_EXPORT int ts_qkv_prepare(const void* proj, int act_dtype, long long ld, int 
   const float2* tb = reinterpret_cast<const float2*>(table);
   if (act_dtype == TS_DTYPE_F32)
     return ts_launch(qkv_prepare_kernel<float>, dim3(blocks), dim3(QP_WARPS * 32), 0, s, (const float*)proj, ld, q_off, k_off, v_off, q_bias,
-                     k_bias, v_bias, tb, rot, unit_norm, eps, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, T, nq, nkv, d, e, D);
+                     k_bias, v_bias, tb, rot, unit_norm, eps, (float*)q_out, (float*)k_dst, (float*)v_dst, slot_mapping, T, nq, nkv, d, e, D, positions, qt_coef, qt_every);
   if (act_dtype == TS_DTYPE_BF16)
     return ts_launch(qkv_prepare_kernel<__nv_bfloat16>, dim3(blocks), dim3(QP_WARPS * 32), 0, s, (const __nv_bfloat16*)proj, ld, q_off, k_off,
                      v_off, q_bias, k_bias, v_bias, tb, rot, unit_norm, eps, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_dst,
-                     (__nv_bfloat16*)v_dst, slot_mapping, T, nq, nkv, d, e, D);
+                     (__nv_bfloat16*)v_dst, slot_mapping, T, nq, nkv, d, e, D, positions, qt_coef, qt_every);
   return TS_ERR_BAD_ARGUMENT;
 }
 

@@ -288,3 +288,17 @@ TS_EXPORT int ts_scale_rows(float* x, long long n, float factor, void* stream) {
   const unsigned blocks = (unsigned)min((n + 255) / 256, (long long)148 * 16);
   return ts_launch(scale_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, n, factor);
 }
+
+// x[i] = cap * tanh(x[i] / cap), float32 (logits bent through a soft cap)
+__global__ void softcap_rows_kernel(float* __restrict__ x, long long n, float cap, float inv_cap) {
+  ts_pdl_prologue();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+
+TS_EXPORT int ts_softcap_rows(float* x, long long n, float cap, void* stream) {
+  if (n <= 0) return 0;
+  if (!(cap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)min((n + 255) / 256, (long long)148 * 16);
+  return ts_launch(softcap_rows_kernel, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, x, n, cap, 1.f / cap);
+}

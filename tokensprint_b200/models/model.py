@@ -78,6 +78,18 @@ class Model:
         # hands forward() one LayerCache per run and then one per entry of `extra_caches`.
         self.extra_caches: list[int] = []
         self._embedding_cache: Optional[int] = None
+        # A block that keeps something per request itself (Block.state_need) gets, for every run of
+        # it, a state of its own among the extra caches: a run that reads another run's pages still
+        # has its own block state.
+        self._block_cache: dict[int, int] = {}
+        for i, run in enumerate(spec.run_order):
+            need = self.blocks[run.layer].state_need()
+            if need is not None:
+                if need.kind != "none" or need.state_shape is None:
+                    raise ValueError(f"layer {run.layer}: a block's own state is a slot without pages")
+                self.cache_plan.append(CachePlanEntry(need, i))
+                self._block_cache[i] = len(spec.run_order) + len(self.extra_caches)
+                self.extra_caches.append(len(self.cache_plan) - 1)
         if self.embedding_transform is not None:
             need = self.embedding_transform.cache_need()
             if need.kind != "none" or need.state_shape is not None:
@@ -165,6 +177,8 @@ class Model:
             block = self.blocks[run.layer]
             if not block.reads_through_ops:
                 ops.flush_gemm_chain()
+            if i in self._block_cache:
+                caches[i].block_state = caches[self._block_cache[i]].state
             pending = block.forward(hidden, pending, step, caches[i])
         step.weight_after = step.norm_after = None
         return hidden, pending

@@ -35,7 +35,8 @@ _SIGNATURES = {
     ],
     "ts_attention_paged_simple": [
         _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
-        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_void_p,
+        _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_void_p, _c_void_p,
+        _c_void_p,
     ],
     "ts_sample": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p],
     "ts_sgemm_nt": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_ll, _c_ll, _c_ll, _c_void_p],
@@ -45,14 +46,15 @@ _SIGNATURES = {
     "ts_rmsnorm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_void_p],
     "ts_round_rows": [_c_void_p, _c_int, _c_void_p, _c_int, _c_ll, _c_void_p],
     "ts_latent_prepare": [_c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float,
-                          _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                          _c_void_p, _c_int, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_void_p, _c_ll, _c_void_p],
     "ts_latent_attention_simple": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int,
                                    _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void_p],
     "ts_gelu_tanh": [_c_void_p, _c_void_p, _c_int, _c_ll, _c_void_p],
     "ts_capped_glu": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "ts_gelu_gate_rows": [_c_void_p, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_ll, _c_int, _c_int, _c_void_p],
-    "ts_router_topk": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
-    "ts_router": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p],
+    "ts_router_topk": [_c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "ts_router": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p,
+                  _c_void_p],
     "ts_moe_gate_up_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_float, _c_float, _c_int, _c_int, _c_void_p],
     "ts_moe_down_mma": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
@@ -69,7 +71,7 @@ _SIGNATURES = {
     "ts_branch_norm_add": [_c_void_p, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_float, _c_float,
                            _c_void_p],
     "ts_stream_add": [_c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_void_p],
-    "ts_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_moe_combine": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p, _c_void_p],
 }
 
 _functions: dict[str, object] = {}
@@ -406,6 +408,7 @@ def attention_paged_simple(
     sink: Optional[float] = None,
     softcap: float = 0.0,
     head_sinks: Optional[torch.Tensor] = None,
+    distance: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
 ) -> None:
     """Causal attention over the paged cache on CUDA cores (float32 or bfloat16).
 
@@ -414,9 +417,15 @@ def attention_paged_simple(
     chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count
     from position 0).  sink: a score that joins every softmax's denominator without a value;
     head_sinks [nq] float32: one such score per query head.  softcap > 0: the scaled score goes
-    through softcap * tanh(s / softcap).
+    through softcap * tanh(s / softcap).  distance = (r1, r2), [nq] float32 each: the score of key j
+    loses r1 * ln(1 + r2 * (position - j)).
     """
     flush_gemm_chain()
+    if distance is not None:
+        for name, t in zip(("distance r1", "distance r2"), distance):
+            _cuda_contig(name, t, torch.float32)
+            if t.numel() != num_heads:
+                raise KernelError(f"attention: {name} must have one entry per query head ({num_heads}), got {t.numel()}")
     if head_sinks is not None:
         _cuda_contig("head_sinks", head_sinks, torch.float32)
         if head_sinks.numel() != num_heads:
@@ -444,7 +453,8 @@ def attention_paged_simple(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _act_code("q", q), out.data_ptr(),
         positions.data_ptr(), seq_index.data_ptr(), block_table.data_ptr(), block_table.shape[1],
         page_size, T, nq, nkv, d, float(scale), int(window), int(chunk), 0 if sink is None else 1,
-        0.0 if sink is None else float(sink), float(softcap), _ptr(head_sinks), _stream()))
+        0.0 if sink is None else float(sink), float(softcap), _ptr(head_sinks),
+        None if distance is None else distance[0].data_ptr(), None if distance is None else distance[1].data_ptr(), _stream()))
 
 
 def sample(
@@ -781,7 +791,13 @@ _SIGNATURES.update({
     "ts_scale_rows": [_c_void_p, _c_ll, _c_float, _c_void_p],
     "ts_rope_table": [_c_void_p, _c_void_p, _c_float, _c_int, _c_int, _c_void_p, _c_void_p],
     "ts_qkv_prepare": [_c_void_p, _c_int, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_float,
-                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+                       _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_float, _c_int,
+                       _c_void_p],
+    "ts_softcap_rows": [_c_void_p, _c_ll, _c_float, _c_void_p],
+    "ts_causal_conv": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                       _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void_p],
+    "ts_delta_scan": [_c_void_p, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
+                      _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
     "ts_gate_rows": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_weighted_sum": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_float, _c_float, _c_float, _c_int, _c_void_p, _c_int, _c_ll,
                         _c_void_p],
@@ -973,6 +989,89 @@ def scale_rows(x: torch.Tensor, factor: float) -> None:
     _check("scale_rows", _fn("ts_scale_rows")(x.data_ptr(), x.numel(), float(factor), _stream()))
 
 
+def softcap_rows(x: torch.Tensor, cap: float) -> None:
+    """x = cap * tanh(x / cap) in place, float32."""
+    flush_gemm_chain()
+    _cuda_contig("x", x, torch.float32)
+    if not cap > 0:
+        raise KernelError("softcap_rows: the cap must be positive")
+    _check("softcap_rows", _fn("ts_softcap_rows")(x.data_ptr(), x.numel(), float(cap), _stream()))
+
+
+CONV_ACTIVATIONS = {None: 0, "silu": 1}
+
+
+def causal_conv(xin: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tensor], conv_state: Optional[torch.Tensor], state_slots: torch.Tensor,
+                cu_seqlens: torch.Tensor, seq_index: torch.Tensor, num_seqs: int, out: torch.Tensor, activation: Optional[str] = None,
+                add_input: bool = False) -> None:
+    """A short causal convolution over time on every channel of xin [T, C] (a view of a wider matrix
+    is fine): out[t] = act(sum_j taps[:, j] * x[t - (K-1) + j] + bias), or with `add_input`
+    x[t] + that.  taps [C, K] float32 (the last column weighs the current token), bias [C] float32 or
+    None.  conv_state [slots, >= (K-1)*C] float32 (a view with a row stride is fine) holds the last
+    K - 1 inputs of every request, oldest first; it is read for the inputs before a portion and then
+    brought up to date with the portion's last inputs (K = 1: there is none, and conv_state may be None).
+    Sums in float32; xin and out may differ in type."""
+    flush_gemm_chain()
+    T, C = xin.shape
+    K = taps.shape[1]
+    _matrix_view("causal_conv: xin", xin, T, C)
+    _matrix_view("causal_conv: out", out, T, C)
+    _cuda_contig("taps", taps, torch.float32)
+    if taps.shape != (C, K):
+        raise KernelError(f"causal_conv: taps must be [{C}, K], got {tuple(taps.shape)}")
+    if bias is not None:
+        _cuda_contig("bias", bias, torch.float32)
+    if K > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 2 or conv_state.stride(1) != 1
+                  or conv_state.shape[1] < (K - 1) * C):
+        raise KernelError(f"causal_conv: the state must be float32 [slots, >= {(K - 1) * C}]")
+    state_ptr, state_stride = (None, 0) if K == 1 else (conv_state.data_ptr(), conv_state.stride(0))
+    if activation not in CONV_ACTIVATIONS:
+        raise KernelError(f"causal_conv: activation must be one of {list(CONV_ACTIVATIONS)}, got {activation!r}")
+    _check("causal_conv", _fn("ts_causal_conv")(
+        xin.data_ptr(), _act_code("xin", xin), xin.stride(0), taps.data_ptr(), _ptr(bias), K, state_ptr, state_stride,
+        state_slots.data_ptr(), cu_seqlens.data_ptr(), seq_index.data_ptr(), out.data_ptr(), _act_code("out", out), out.stride(0), T, C,
+        CONV_ACTIVATIONS[activation], 1 if add_input else 0, _stream()))
+    if K > 1:
+        _check("ssm_conv_state", _fn("ts_ssm_conv_state")(xin.data_ptr(), _act_code("xin", xin), xin.stride(0), K, state_ptr, state_stride,
+                                                          state_slots.data_ptr(), cu_seqlens.data_ptr(), int(num_seqs), C, _stream()))
+
+
+DELTA_MAX_KEY_DIM = 1024
+
+
+def delta_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
+               state: torch.Tensor, state_slots: torch.Tensor, cu_seqlens: torch.Tensor, out: torch.Tensor, num_seqs: int, num_heads: int,
+               num_qk_heads: int, key_dim: int, value_dim: int, q_scale: float, unit_eps: float) -> None:
+    """The gated delta rule over the tokens of every sequence, in order (csrc/delta_rule.cu).  x [T, n]
+    float32 holds q (columns q_off.., num_qk_heads * key_dim), k (k_off..) and v (v_off.., num_heads *
+    value_dim); q and k are brought to unit length per head here and q is multiplied by q_scale.
+    gates [T, 2 * heads] float32: the raw write-strength rows, then the raw decay rows (beta = sigmoid,
+    decay = exp(-exp(a_log) * softplus(raw + dt_bias))).  state [slots, >= heads * value_dim * key_dim]
+    float32 (a view with a row stride is fine), one head after the other, value column by value column;
+    out [T, heads * value_dim] float32."""
+    flush_gemm_chain()
+    H, G, d, e = int(num_heads), int(num_qk_heads), int(key_dim), int(value_dim)
+    T = x.shape[0]
+    if not x.is_cuda or x.dtype != torch.float32 or x.dim() != 2 or x.stride(1) != 1:
+        raise KernelError("delta_scan: x must be a float32 CUDA matrix with unit inner stride")
+    if max(q_off, k_off) + G * d > x.shape[1] or v_off + H * e > x.shape[1]:
+        raise KernelError("delta_scan: the column ranges do not fit x")
+    _matrix_view("delta_scan: gates", gates, T, 2 * H, torch.float32)
+    _cuda_contig("a_log", a_log, torch.float32)
+    _cuda_contig("dt_bias", dt_bias, torch.float32)
+    _cuda_contig("out", out, torch.float32)
+    if a_log.numel() != H or dt_bias.numel() != H or out.shape != (T, H * e):
+        raise KernelError("delta_scan: a_log and dt_bias need one entry per head, out must be [T, heads * value_dim]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.stride(1) != 1 or state.shape[1] < H * d * e:
+        raise KernelError(f"delta_scan: the state must be float32 [slots, >= {H * d * e}], got {tuple(state.shape)}")
+    if d > DELTA_MAX_KEY_DIM or H % G:
+        raise KernelError(f"delta_scan: key_dim at most {DELTA_MAX_KEY_DIM}, heads a multiple of the q/k heads")
+    _check("delta_scan", _fn("ts_delta_scan")(
+        x.data_ptr(), x.stride(0), int(q_off), int(k_off), int(v_off), gates.data_ptr(), gates.stride(0), a_log.data_ptr(), dt_bias.data_ptr(),
+        state.data_ptr(), state.stride(0), state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, G, d, e,
+        float(q_scale), float(unit_eps), _stream()))
+
+
 WEIGHTED_SUM_MAX_INPUTS = 4
 
 
@@ -1016,14 +1115,24 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, magnitude: float
 def qkv_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_bias: Optional[torch.Tensor], k_bias: Optional[torch.Tensor],
                 v_bias: Optional[torch.Tensor], table: Optional[torch.Tensor], unit_norm: bool, eps: float, q_out: torch.Tensor,
                 k_dst: Optional[torch.Tensor], v_dst: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor], num_heads: int,
-                num_kv_heads: int, key_dim: int, value_dim: int, padded_dim: int) -> None:
+                num_kv_heads: int, key_dim: int, value_dim: int, padded_dim: int, positions: Optional[torch.Tensor] = None,
+                query_temperature: Optional[tuple[float, int]] = None) -> None:
     """Queries, keys and values of a step out of one projection's result `proj` [T, n] (columns q_off..,
     k_off.., v_off..): biases [heads*dim] float32 (or None), rotation of the first 2*table.shape[1]
     entries of every q and k head by the table's (cos, sin) (rope_table; None: no rotation), then with
     `unit_norm` q and k heads divided by sqrt(mean(x^2) + eps).  q_out [T, nq, D]; keys and values go to
     k_dst / v_dst [slots, nkv, D] at slot_mapping[t] (None: row t; a negative slot: not kept), padded with
-    zeros from their own width to D = padded_dim.  k_dst None: only the queries are made."""
+    zeros from their own width to D = padded_dim.  k_dst None: only the queries are made.
+    query_temperature = (coef, every) with the tokens' positions: query heads are multiplied by
+    1 + coef * ln(floor((position + 1) / every) + 1)."""
     flush_gemm_chain()
+    qt_coef, qt_every = (0.0, 0) if query_temperature is None else (float(query_temperature[0]), int(query_temperature[1]))
+    if qt_every:
+        if qt_every < 1 or positions is None:
+            raise KernelError("qkv_prepare: a query temperature needs the positions and a positive step")
+        _cuda_contig("positions", positions, torch.int32)
+        if positions.numel() < proj.shape[0]:
+            raise KernelError("qkv_prepare: positions are shorter than the tokens")
     nq, nkv, d, e, D = int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim), int(padded_dim)
     T = proj.shape[0]
     if not proj.is_cuda or proj.dim() != 2 or proj.stride(1) != 1:
@@ -1055,7 +1164,7 @@ def qkv_prepare(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, q_bias: 
     _check("qkv_prepare", _fn("ts_qkv_prepare")(
         proj.data_ptr(), _act_code("proj", proj), proj.stride(0), int(q_off), int(k_off), int(v_off), _ptr(q_bias), _ptr(k_bias), _ptr(v_bias),
         _ptr(table), rot, 1 if unit_norm else 0, float(eps), q_out.data_ptr(), _ptr(k_dst), _ptr(v_dst), _ptr(slot_mapping), T, nq, kv_heads,
-        d, e, D, _stream()))
+        d, e, D, _ptr(positions) if qt_every else None, qt_coef, qt_every, _stream()))
 
 
 def gate_rows(a: torch.Tensor, gate: Optional[torch.Tensor], out: torch.Tensor, num_heads: int, value_dim: int, padded_dim: int) -> None:
@@ -1077,30 +1186,46 @@ ROTARY_PAIRINGS = {"half": 0, "neighbours": 1}
 LATENT_SIMPLE_MAX_KEY_DIM = 1024
 
 
-def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gate_off: int, q_abs: torch.Tensor, cache: Optional[torch.Tensor],
-                   slot_mapping: Optional[torch.Tensor], positions: torch.Tensor, latent_weight: torch.Tensor, eps: float,
+def latent_prepare(proj: Optional[torch.Tensor], q_off: int, kv_off: int, gate_off: int, q_abs: torch.Tensor, cache: Optional[torch.Tensor],
+                   slot_mapping: Optional[torch.Tensor], positions: torch.Tensor, latent_weight: Optional[torch.Tensor], eps: float,
                    inv_freq: Optional[torch.Tensor], rot_dims: int, pairing: str, gates: Optional[torch.Tensor], num_heads: int,
-                   nope_dim: int, rot_dim: int, rank: int) -> None:
+                   nope_dim: int, rot_dim: int, rank: int, magnitude: float = 1.0, q_src: Optional[torch.Tensor] = None) -> None:
     """What follows the stacked projection of a latent attention layer, per token: the latent (columns
     kv_off .. kv_off+rank of `proj`) RMS-normed with `latent_weight`, the key part behind it and
     every head's rotated query part turned by the token's position, [latent ; key part] stored in
     `cache` [slots, rank+rot] at slot_mapping[t] (-1 or no mapping: not stored), the rotated query
-    parts written to q_abs[t, head, rank:], and gates[t, head] = sigmoid(proj[t, gate_off+head])."""
+    parts written to q_abs[t, head, rank:], and gates[t, head] = sigmoid(proj[t, gate_off+head]).
+    Cosines and sines are multiplied by `magnitude`.  `q_src` [T, heads*(nope+rot)]: the queries come
+    from this tensor instead of proj's columns from q_off on.  kv_off < 0: the layer has no latent of
+    its own (it reads rows that another layer cached): only the queries are prepared, and `proj` may
+    then be None."""
     flush_gemm_chain()
-    _cuda_contig("proj", proj)
-    _cuda_contig("q_abs", q_abs, proj.dtype)
-    _cuda_contig("positions", positions, torch.int32)
-    _cuda_contig("latent_weight", latent_weight, torch.float32)
-    T, ld = proj.shape
     H, dn, dr = num_heads, nope_dim, rot_dim
+    if q_src is not None:
+        _cuda_contig("q_src", q_src, q_abs.dtype)
+        if q_src.dim() != 2 or q_src.shape[1] != H * (dn + dr):
+            raise KernelError(f"latent_prepare: q_src must be [T, {H * (dn + dr)}], got {tuple(q_src.shape)}")
+    if proj is None:
+        if q_src is None or kv_off >= 0 or gates is not None or cache is not None:
+            raise KernelError("latent_prepare: without a projection only queries from q_src are prepared")
+        T, ld = q_src.shape[0], 0
+    else:
+        _cuda_contig("proj", proj, q_abs.dtype)
+        T, ld = proj.shape
+    _cuda_contig("q_abs", q_abs)
+    _cuda_contig("positions", positions, torch.int32)
+    if kv_off >= 0:
+        _cuda_contig("latent_weight", latent_weight, torch.float32)
+    elif cache is not None or slot_mapping is not None:
+        raise KernelError("latent_prepare: a layer without a latent of its own stores nothing")
     if q_abs.numel() != T * H * (rank + dr):
         raise KernelError(f"latent_prepare: q_abs must hold [{T}, {H}, {rank + dr}], got {tuple(q_abs.shape)}")
-    if q_off + H * (dn + dr) > ld or kv_off + rank + dr > ld or (gates is not None and gate_off + H > ld):
+    if (q_src is None and q_off + H * (dn + dr) > ld) or (kv_off >= 0 and kv_off + rank + dr > ld) or (gates is not None and gate_off + H > ld):
         raise KernelError("latent_prepare: the column ranges do not fit the projection's width")
     if slot_mapping is not None:
         if cache is None:
             raise KernelError("latent_prepare: a slot mapping needs the cache")
-        _cuda_contig("cache", cache, proj.dtype)
+        _cuda_contig("cache", cache, q_abs.dtype)
         _cuda_contig("slot_mapping", slot_mapping, torch.int32)
         if cache.shape[-1] != rank + dr or slot_mapping.numel() < T:
             raise KernelError(f"latent_prepare: cache rows must be {rank + dr} wide and slot_mapping hold {T} entries")
@@ -1115,9 +1240,10 @@ def latent_prepare(proj: torch.Tensor, q_off: int, kv_off: int, gate_off: int, q
         if inv_freq.numel() != rot_dims // 2 or rot_dims > dr or rot_dims % 2:
             raise KernelError(f"latent_prepare: {rot_dims} rotated entries of {dr} need {rot_dims // 2} frequencies")
     _check("latent_prepare", _fn("ts_latent_prepare")(
-        proj.data_ptr(), _act_code("proj", proj), ld, int(q_off), int(kv_off), int(gate_off), q_abs.data_ptr(), _ptr(cache),
-        _ptr(slot_mapping), positions.data_ptr(), latent_weight.data_ptr(), float(eps), _ptr(inv_freq), int(rot_dims),
-        ROTARY_PAIRINGS[pairing], _ptr(gates), T, H, dn, dr, int(rank), _stream()))
+        _ptr(proj), _act_code("q_abs", q_abs), ld, int(q_off), int(kv_off), int(gate_off), q_abs.data_ptr(), _ptr(cache),
+        _ptr(slot_mapping), positions.data_ptr(), _ptr(latent_weight), float(eps), _ptr(inv_freq), int(rot_dims),
+        ROTARY_PAIRINGS[pairing], _ptr(gates), T, H, dn, dr, int(rank), float(magnitude), _ptr(q_src),
+        0 if q_src is None else q_src.stride(0), _stream()))
 
 
 def latent_attention_simple(q_abs: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, gates: Optional[torch.Tensor],
@@ -1189,7 +1315,7 @@ MOE_ROW_TILE = 64
 MOE_MAX_EXPERTS = 4096
 
 
-ROUTER_SCORES = {"sigmoid": 0, "softmax_chosen": 1}
+ROUTER_SCORES = {"sigmoid": 0, "softmax_chosen": 1, "softmax_all": 2}
 
 
 def _router_bias(name: str, bias: Optional[torch.Tensor], E: int) -> Optional[int]:
@@ -1202,11 +1328,12 @@ def _router_bias(name: str, bias: Optional[torch.Tensor], E: int) -> Optional[in
 
 
 def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
-                bias: Optional[torch.Tensor] = None, score: str = "sigmoid") -> None:
+                bias: Optional[torch.Tensor] = None, score: str = "sigmoid", correction: Optional[torch.Tensor] = None) -> None:
     """Per row of float32 logits [T, E] (+ bias [E], if given): the `top` experts with the largest
     logits into ids [T, top] i32 and their weights into weights [T, top] f32.  score "sigmoid": the
     weights are sigmoid(logit) (divided by their sum if `renormalize`); "softmax_chosen": the softmax
-    over the chosen logits alone."""
+    over the chosen logits alone; "softmax_all": the scores are the softmax over all E logits, the
+    `top` largest of score + correction [E] are chosen, and the weights are the scores themselves."""
     flush_gemm_chain()
     _cuda_contig("logits", logits, torch.float32)
     _cuda_contig("ids", ids, torch.int32)
@@ -1215,11 +1342,18 @@ def router_topk(logits: torch.Tensor, top: int, renormalize: bool, ids: torch.Te
     if not 0 < top <= E or ids.numel() != T * top or weights.numel() != T * top:
         raise KernelError(f"router_topk: top {top} of {E} experts, ids {tuple(ids.shape)}, weights {tuple(weights.shape)}")
     _check("router_topk", _fn("ts_router_topk")(logits.data_ptr(), _router_bias("router_topk", bias, E), T, E, int(top),
-                                                int(bool(renormalize)), ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(), _stream()))
+                                                int(bool(renormalize)), ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(),
+                                                _router_correction("router_topk", correction, E, score), _stream()))
+
+
+def _router_correction(name: str, correction: Optional[torch.Tensor], E: int, score: str) -> Optional[int]:
+    if correction is not None and score != "softmax_all":
+        raise KernelError(f"{name}: a correction of the choice comes with the scores 'softmax_all' only")
+    return _router_bias(name, correction, E)
 
 
 def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormalize: bool, ids: torch.Tensor, weights: torch.Tensor,
-           bias: Optional[torch.Tensor] = None, score: str = "sigmoid") -> None:
+           bias: Optional[torch.Tensor] = None, score: str = "sigmoid", correction: Optional[torch.Tensor] = None) -> None:
     """Logits and choice in one kernel: rows [T, W] (float32, or bfloat16 widened on the fly) against
     router_weight [E, W] float32 with float32 sums (+ bias [E] float32, if given), then as router_topk."""
     flush_gemm_chain()
@@ -1233,7 +1367,7 @@ def router(rows: torch.Tensor, router_weight: torch.Tensor, top: int, renormaliz
         raise KernelError(f"router: rows {tuple(rows.shape)}, router {tuple(router_weight.shape)}, top {top}, ids {tuple(ids.shape)}")
     _check("router", _fn("ts_router")(rows.data_ptr(), _act_code("rows", rows), router_weight.data_ptr(), _router_bias("router", bias, E),
                                       T, W, E, int(top), int(bool(renormalize)), ROUTER_SCORES[score], ids.data_ptr(), weights.data_ptr(),
-                                      _stream()))
+                                      _router_correction("router", correction, E, score), _stream()))
 
 
 # TS_MOE_MMA=0 (for measurements): bfloat16 expert products on CUDA cores too.
@@ -1290,34 +1424,41 @@ def _moe_path(name: str, plan, dtype: torch.dtype, *inner_widths: int) -> bool:
     raise KernelError(f"{name}: the plan was made for row tiles of {plan[3]}, which no kernel for {dtype} and inner widths {inner_widths} takes")
 
 
-MOE_ACTIVATIONS = {"capped_glu": 0, "swiglu": 1}
+MOE_ACTIVATIONS = {"capped_glu": 0, "swiglu": 1, "gelu": 2}  # "gelu": experts without a gate matrix, W_down gelu_erf(W_up x)
 
 
-def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple, gate: torch.Tensor,
+def moe_gate_up(x: torch.Tensor, pair_weight: torch.Tensor, plan: tuple, gate: Optional[torch.Tensor],
                 up: torch.Tensor, act: torch.Tensor, top: int, limit: float, alpha: float, activation: str = "capped_glu") -> None:
     """For every pair, in the plan's order: act[place] = activation(gate_e (w x[token]), up_e (w x[token])), where
-    activation is "capped_glu" (with `limit` and `alpha`) or "swiglu" (silu(gate) * up).
+    activation is "capped_glu" (with `limit` and `alpha`) or "swiglu" (silu(gate) * up); or, for experts
+    without a gate matrix (`gate` None, activation "gelu"), act[place] = gelu_erf(up_e (w x[token])).
     x [T, K]; pair_weight [T*top] f32; gate, up [E, I, K]; act [T*top, I]."""
     flush_gemm_chain()
     offsets, tile_offsets, order, _ = plan
     _cuda_contig("x", x)
-    _cuda_contig("gate", gate, x.dtype)
+    if (gate is None) != (activation == "gelu"):
+        raise KernelError("moe_gate_up: the activation 'gelu' comes without a gate matrix, the gated ones with one")
+    if gate is None:
+        gate_ptr = None
+    else:
+        _cuda_contig("gate", gate, x.dtype)
+        gate_ptr = gate.data_ptr()
     _cuda_contig("up", up, x.dtype)
     _cuda_contig("act", act, x.dtype)
     _cuda_contig("pair_weight", pair_weight, torch.float32)
     T, K = x.shape
-    E, I, K2 = gate.shape
+    E, I, K2 = up.shape
     P = T * top
-    if K2 != K or up.shape != gate.shape or act.shape != (P, I) or pair_weight.numel() != P or order.numel() != P:
-        raise KernelError(f"moe_gate_up: shapes disagree: x {tuple(x.shape)}, gate {tuple(gate.shape)}, up {tuple(up.shape)}, act {tuple(act.shape)}")
+    if K2 != K or (gate is not None and up.shape != gate.shape) or act.shape != (P, I) or pair_weight.numel() != P or order.numel() != P:
+        raise KernelError(f"moe_gate_up: shapes disagree: x {tuple(x.shape)}, up {tuple(up.shape)}, act {tuple(act.shape)}")
     if _moe_path("moe_gate_up", plan, x.dtype, K):
         _check("moe_gate_up", _fn("ts_moe_gate_up_mma")(
-            x.data_ptr(), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), gate.data_ptr(),
+            x.data_ptr(), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(), gate_ptr,
             up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), MOE_ACTIVATIONS[activation], plan[3], _stream()))
         return
     _check("moe_gate_up", _fn("ts_moe_gate_up")(
         x.data_ptr(), _act_code("x", x), pair_weight.data_ptr(), order.data_ptr(), offsets.data_ptr(), tile_offsets.data_ptr(),
-        gate.data_ptr(), up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), MOE_ACTIVATIONS[activation], _stream()))
+        gate_ptr, up.data_ptr(), act.data_ptr(), P, E, K, I, int(top), float(limit), float(alpha), MOE_ACTIVATIONS[activation], _stream()))
 
 
 def moe_down(act: torch.Tensor, plan: tuple, down: torch.Tensor, pair_out: torch.Tensor) -> None:
@@ -1342,9 +1483,12 @@ def moe_down(act: torch.Tensor, plan: tuple, down: torch.Tensor, pair_out: torch
 
 
 def moe_combine(pair_out: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor, top: int,
-                pair_weight: Optional[torch.Tensor] = None) -> None:
+                pair_weight: Optional[torch.Tensor] = None, ids: Optional[torch.Tensor] = None, num_experts: int = 0,
+                x: Optional[torch.Tensor] = None) -> None:
     """out[t] = sum of pair_out[t*top .. t*top+top] (each times pair_weight[pair] if given) (+ shared[t]),
-    summed in float32."""
+    summed in float32.  With `ids` [T, top] i32, `num_experts` and the experts' input rows `x` [T, N], a
+    pair whose chosen index is num_experts or more is an identity expert: x[t] stands in for its row of
+    pair_out (which nothing has written)."""
     flush_gemm_chain()
     _cuda_contig("pair_out", pair_out)
     _cuda_contig("out", out, pair_out.dtype)
@@ -1359,8 +1503,15 @@ def moe_combine(pair_out: torch.Tensor, shared: Optional[torch.Tensor], out: tor
         _cuda_contig("pair_weight", pair_weight, torch.float32)
         if pair_weight.numel() != T * top:
             raise KernelError("moe_combine: one weight per pair is needed")
+    if ids is not None:
+        _cuda_contig("ids", ids, torch.int32)
+        if x is None or ids.numel() != T * top:
+            raise KernelError("moe_combine: identity experts need the chosen indices of every pair and the input rows")
+        _cuda_contig("x", x, out.dtype)
+        if x.shape != out.shape:
+            raise KernelError("moe_combine: x must have out's shape")
     _check("moe_combine", _fn("ts_moe_combine")(pair_out.data_ptr(), _ptr(shared), out.data_ptr(), _ptr(pair_weight), _act_code("out", out),
-                                                T, N, int(top), _stream()))
+                                                T, N, int(top), _ptr(ids), int(num_experts), _ptr(x) if ids is not None else None, _stream()))
 
 
 # ---------------------------------------------------------------------------
@@ -1500,6 +1651,7 @@ def _attention_error_word() -> torch.Tensor:
 
 ATTENTION_MMA_MAX_HEAD_DIM = 256
 ATTENTION_MMA_MAX_SPLITS = 64
+ATTENTION_MMA_DISTANCE = False  # whether the tensor-core kernels know the logarithmic distance penalty
 _attention_mma: dict[int, tuple] = {}
 
 
@@ -1653,6 +1805,7 @@ def attention_paged_mma(
     sink: Optional[float] = None,
     softcap: float = 0.0,
     head_sinks: Optional[torch.Tensor] = None,
+    distance: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
 ) -> None:
     """Causal attention over the paged cache on tensor cores (bfloat16).
 
@@ -1669,7 +1822,9 @@ def attention_paged_mma(
     softcap * tanh(s / softcap).
     """
     flush_gemm_chain()
-    scored = head_sinks is not None or softcap > 0.0
+    if distance is not None and not ATTENTION_MMA_DISTANCE:
+        raise KernelError("attention_paged_mma: this build knows no distance penalty")
+    scored = head_sinks is not None or softcap > 0.0 or distance is not None
     run, _ = _attention_mma_fns(head_dim, scored)
     if head_sinks is not None:
         _cuda_contig("head_sinks", head_sinks, torch.float32)

@@ -2,7 +2,7 @@
 
 from __future__ import annotations
 
-from typing import Mapping, Optional
+from typing import Mapping, Optional, Sequence
 
 import torch
 
@@ -52,6 +52,11 @@ class AttentionMixer(Mixer):
     `value_dim`: values (and the heads the output projection reads) of another width than keys.
     `gate` = name of a [num_heads * value_dim, hidden] matrix: the concatenated heads are multiplied
     by sigmoid(gate x) before the output projection.
+    `q_temperature` = (coef, every): the queries at position p are multiplied by
+    1 + coef * ln(floor((p + 1) / every) + 1).
+    `distance` = (name r1, name r2) of two [num_heads] tensors: the scaled score of key j for the query
+    at position i loses r1_h * ln(1 + r2_h * (i - j)), a penalty per head that grows with the logarithm
+    of the distance (positions enter such a layer through it, and through the temperature, alone).
     A position encoding whose cosines and sines carry a magnitude is applied from its table.
     With any of the options from `sinks` on, one product gives [q | k | v | gate], `qkv_prepare`
     adds biases, rotates, norms and stores (keys and values padded with zeros to one common width
@@ -92,6 +97,8 @@ class AttentionMixer(Mixer):
         v_bias: Optional[str] = None,
         value_dim: Optional[int] = None,
         gate: Optional[str] = None,
+        q_temperature: Optional[Sequence[float]] = None,
+        distance: Optional[Sequence[str]] = None,
     ) -> None:
         if qk_norm is True:
             qk_norm = "head"
@@ -104,6 +111,10 @@ class AttentionMixer(Mixer):
             raise ValueError("attention: one sink score for all heads, or a tensor of scores, not both")
         if softcap < 0:
             raise ValueError("attention: softcap must not be negative")
+        if q_temperature is not None and (len(q_temperature) != 2 or int(q_temperature[1]) < 1):
+            raise ValueError("attention: q_temperature is (coef, every) with every >= 1")
+        if distance is not None and len(distance) != 2:
+            raise ValueError("attention: distance names two tensors (r1, r2)")
         if values not in ("projection", "keys"):
             raise ValueError(f"attention: values must be 'projection' or 'keys', got {values!r}")
         if (values == "projection") != (v is not None):
@@ -125,14 +136,17 @@ class AttentionMixer(Mixer):
             raise ValueError("attention: chunk must not be negative")
         self.scale = float(scale) if scale is not None else float(head_dim) ** -0.5
         self.names = {"q": q, "k": k, "v": v, "o": o, "q_norm": q_norm, "k_norm": k_norm, "sinks": sinks, "q_bias": q_bias,
-                      "k_bias": k_bias, "v_bias": v_bias, "gate": gate}
+                      "k_bias": k_bias, "v_bias": v_bias, "gate": gate,
+                      "r1": None if distance is None else distance[0], "r2": None if distance is None else distance[1]}
+        self.q_temperature = None if q_temperature is None else (float(q_temperature[0]), int(q_temperature[1]))
+        self.distance: Optional[tuple[torch.Tensor, torch.Tensor]] = None
         self.position = build_part("position_encoding", position, ctx) if position is not None else None
         self.unit_after_rotation, self.softcap = unit_after, float(softcap)
         self.value_dim = self.head_dim if value_dim is None else int(value_dim)
         magnitude = getattr(self.position, "magnitude", 1.0) if self.position is not None else 1.0
         # the path through qkv_prepare (see the class's text)
         self.general = bool(unit_after or sinks or softcap or q_bias or k_bias or v_bias or gate or self.value_dim != self.head_dim
-                            or magnitude != 1.0)
+                            or magnitude != 1.0 or q_temperature is not None or distance is not None)
         # the width the attention kernels run at: the wider of keys and values, and in bfloat16 the next
         # multiple of 16 (what the tensor-core kernels take): entries beyond a head's own are zeros
         self.kernel_dim = self.head_dim
@@ -186,6 +200,8 @@ class AttentionMixer(Mixer):
             specs.append(TensorSpec(n["gate"], (nq * e, H)))
         if n["sinks"] is not None:
             specs.append(TensorSpec(n["sinks"], (nq,), "vector"))
+        if n["r1"] is not None:
+            specs += [TensorSpec(n["r1"], (nq,), "vector"), TensorSpec(n["r2"], (nq,), "vector")]
         for key, width in (("q_bias", nq * d), ("k_bias", nkv * d), ("v_bias", nkv * e)):
             if n[key] is not None:
                 specs.append(TensorSpec(n[key], (width,), "vector"))
@@ -204,6 +220,8 @@ class AttentionMixer(Mixer):
         self.qkv_weight = torch.cat(stacked, dim=0).contiguous()
         if n["sinks"] is not None:
             self.head_sinks = tensors[n["sinks"]]
+        if n["r1"] is not None:
+            self.distance = (tensors[n["r1"]], tensors[n["r2"]])
         for key in ("q", "k", "v"):
             if n[key + "_bias"] is not None:
                 self.biases[key] = tensors[n[key + "_bias"]]
@@ -296,7 +314,8 @@ class AttentionMixer(Mixer):
         writes = cache.writes
         ops.qkv_prepare(proj, 0, k_off, v_off, self.biases["q"], self.biases["k"], self.biases["v"], table, self.unit_after_rotation,
                         self.qk_norm_eps, q, cache.k_pages if writes else None, cache.v_pages if writes else None,
-                        tables.slot_mapping if writes else None, nq, nkv, d, e, D)
+                        tables.slot_mapping if writes else None, nq, nkv, d, e, D, positions=step.positions,
+                        query_temperature=self.q_temperature)
         out = torch.empty((T, nq * D), device=x.device, dtype=x.dtype)
         self._attend(q, out, step, cache, tables)
         gated = self.names["gate"] is not None
@@ -311,14 +330,17 @@ class AttentionMixer(Mixer):
     def _attend(self, q, out, step: StepContext, cache: LayerCache, tables) -> None:
         nq, nkv, d = self.num_heads, self.num_kv_heads, self.kernel_dim
         scored = {"softcap": self.softcap, "head_sinks": self.head_sinks}
-        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d):
+        if self.distance is not None:
+            scored["distance"] = self.distance
+        if q.dtype == torch.bfloat16 and ops.attention_mma_supported(d) and (self.distance is None or ops.ATTENTION_MMA_DISTANCE):
             B, singles = step.num_seqs, step.decode_seqs
             few_rows = (nq // nkv) <= ops.attention_decode_rows(d)
             if step.max_seqlen_q * (nq // nkv) <= ops.attention_decode_rows(d):
                 # few rows per sequence: the decode kernels, keys spread over CTAs
                 self._attend_decode(q, out, step, cache, tables, 0, B, step.max_seqlen_q)
                 return
-            prompts_on_tcgen05 = ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
+            # (the tcgen05 kernel knows no distance penalty: such layers run the mma.sync prompt kernel)
+            prompts_on_tcgen05 = self.distance is None and ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
             if prompts_on_tcgen05 and few_rows and 0 < singles < B:
                 # Single decoded tokens beside portions of prompts (the runner put the single tokens'
                 # requests first): each kind to its own kernel.  Through the prompt kernel a decoded
@@ -347,7 +369,7 @@ class AttentionMixer(Mixer):
         ops.attention_paged_simple(
             q, cache.k_pages, cache.v_pages, out, step.positions, step.seq_index, tables.block_table,
             step.page_size, self.num_heads, self.num_kv_heads, d, self.scale, self.window, self.chunk, self.sink,
-            softcap=self.softcap, head_sinks=self.head_sinks)
+            softcap=self.softcap, head_sinks=self.head_sinks, distance=self.distance)
 
     def _attend_decode(self, q, out, step: StepContext, cache: LayerCache, tables, first: int, count: int, max_q: int) -> None:
         """Sequences [first, first + count) of the batch, each with at most `max_q` tokens (few enough
@@ -364,7 +386,7 @@ class AttentionMixer(Mixer):
         context = ops.attention_decode_plan_context(step.max_context_len, reach)
         splits = ops.attention_decode_splits(count, nkv, context, d)
         # (the even-share decode kernel knows neither a block bound nor a sink nor a score cap)
-        if (self.chunk == 0 and self.sink is None and self.head_sinks is None and self.softcap == 0.0
+        if (self.chunk == 0 and self.sink is None and self.head_sinks is None and self.softcap == 0.0 and self.distance is None
                 and ops.attention_decode_prefers_flat(count, nkv, splits, d)
                 and ops.attention_decode_flat_supported(nq, nkv, d, step.page_size, count, max_q)):
             # more (sequence, KV head) pairs than CTAs run at once: an even share of all key blocks per CTA
@@ -377,7 +399,8 @@ class AttentionMixer(Mixer):
             scratch = torch.empty(ops.attention_scratch_floats(q.shape[0] * nq, splits, d), device=q.device, dtype=torch.float32)
         ops.attention_paged_mma(
             q, cache.k_pages, cache.v_pages, out, cu, lens, table, seq_index, step.page_size, count, max_q, nq, nkv, d,
-            self.scale, self.window, splits, scratch, 0, chunk=self.chunk, sink=self.sink, softcap=self.softcap, head_sinks=self.head_sinks)
+            self.scale, self.window, splits, scratch, 0, chunk=self.chunk, sink=self.sink, softcap=self.softcap, head_sinks=self.head_sinks,
+            distance=self.distance)
 
     # -- less common paths ----------------------------------------------------
 

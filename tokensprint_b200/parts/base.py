@@ -208,6 +208,9 @@ class LayerCache:
     v_pages: Optional[torch.Tensor] = None  # [pages, page, *v_row], or None for a cache of one pool
     state: Optional[torch.Tensor] = None  # [slots, *state_shape]
     writes: bool = True  # False: reads a cache that another run filled
+    # [slots, *shape]: what the block around the mixer keeps per request (Block.state_need); always the
+    # run's own, also where the run reads another run's pages
+    block_state: Optional[torch.Tensor] = None
 
 
 # ---------------------------------------------------------------------------
@@ -329,6 +332,12 @@ class Block(Part):
     def entry_norm(self) -> Optional["Norm"]:
         """The norm that reads the residual stream first in this block, if the part before may
         prepare its input (see ResidualNorm); None: nobody may."""
+        return None
+
+    def state_need(self) -> Optional[CacheNeed]:
+        """What the block itself keeps per request between steps, beside its mixer's cache: a
+        CacheNeed without pages whose `state_shape` is the slot's shape, or None.  Every run of the
+        block gets a slot tensor of its own as `LayerCache.block_state` (zeroed at admission)."""
         return None
 
     def forward(

@@ -10,6 +10,7 @@ from tokensprint_b200 import ops
 from tokensprint_b200.parts.base import (
     Block,
     BuildContext,
+    CacheNeed,
     LayerCache,
     Normed,
     PartSpec,
@@ -195,11 +196,18 @@ class SandwichNormBlock(Block):
     absent.  The output norms are plain RMS norms; one kernel runs such a norm on the branch, the
     scale, the sum into the stream and the norm that reads the stream next (this block's
     feed-forward norm, or the first norm of the block that follows, which is then handed the
-    finished rows as a `Normed`)."""
+    finished rows as a `Normed`).
+
+    `mixer_conv` / `ffn_conv` (names of [width, conv_taps] tensors): the sublayer does not read its
+    normed input h but h + conv(h), a short causal convolution over time on every channel (the last
+    tap weighs the current token, zeros before a sequence's start).  The last conv_taps - 1 normed
+    inputs of either sublayer are then part of a request's state: the block keeps them in a slot of
+    its own (`state_need`), so prompts may be cut anywhere."""
 
     def __init__(self, ctx: BuildContext, *, mixer: PartSpec, mixer_norm: PartSpec, mixer_out_norm: PartSpec, hidden_size: int,
                  mixer_scale: Optional[str] = None, feed_forward: Optional[PartSpec] = None, ffn_norm: Optional[PartSpec] = None,
-                 ffn_out_norm: Optional[PartSpec] = None, ffn_scale: Optional[str] = None) -> None:
+                 ffn_out_norm: Optional[PartSpec] = None, ffn_scale: Optional[str] = None, mixer_conv: Optional[str] = None,
+                 ffn_conv: Optional[str] = None, conv_taps: int = 0) -> None:
         if not ((feed_forward is None) == (ffn_norm is None) == (ffn_out_norm is None)):
             raise ValueError("sandwich_norm block: a feed-forward comes with both of its norms")
         if feed_forward is None and ffn_scale is not None:
@@ -212,6 +220,16 @@ class SandwichNormBlock(Block):
         self.ffn_norm = None if ffn_norm is None else build_part("norm", ffn_norm, ctx)
         self.ffn_out_norm = None if ffn_out_norm is None else build_part("norm", ffn_out_norm, ctx)
         self.scale_names = {"mixer": mixer_scale, "ffn": ffn_scale}
+        if feed_forward is None and ffn_conv is not None:
+            raise ValueError("sandwich_norm block: an input convolution without its feed-forward")
+        self.conv_names = {"mixer": mixer_conv, "ffn": ffn_conv}
+        self.conv_taps = int(conv_taps)
+        if (mixer_conv is not None or ffn_conv is not None) and self.conv_taps < 1:
+            raise ValueError("sandwich_norm block: input convolutions need conv_taps >= 1")
+        self.conv_weights: dict[str, Optional[torch.Tensor]] = {"mixer": None, "ffn": None}
+        # the slot's layout: the mixer's kept inputs [conv_taps - 1, width], then the feed-forward's
+        self._conv_floats = (self.conv_taps - 1) * self.hidden_size if self.conv_taps > 1 else 0
+        self._conv_offset = {"mixer": 0, "ffn": self._conv_floats if mixer_conv is not None else 0}
         self.mixer_scale: Optional[torch.Tensor] = None
         self.ffn_scale: Optional[torch.Tensor] = None
         self._parts = tuple(p for p in (self.mixer_norm, self.mixer, self.mixer_out_norm, self.ffn_norm, self.feed_forward, self.ffn_out_norm)
@@ -222,7 +240,29 @@ class SandwichNormBlock(Block):
     def tensor_specs(self) -> list[TensorSpec]:
         specs = [s for p in self._parts for s in p.tensor_specs()]
         specs += [TensorSpec(name, (self.hidden_size,), "vector") for name in self.scale_names.values() if name is not None]
+        specs += [TensorSpec(name, (self.hidden_size, self.conv_taps), "vector") for name in self.conv_names.values() if name is not None]
         return specs
+
+    def state_need(self):
+        convs = sum(1 for name in self.conv_names.values() if name is not None)
+        if not convs or not self._conv_floats:
+            return None
+        return CacheNeed(kind="none", state_shape=(convs * self._conv_floats,), state_dtype=torch.float32)
+
+    def _input_conv(self, which: str, x: torch.Tensor, step: StepContext, cache: LayerCache) -> torch.Tensor:
+        """x + conv(x) for the sublayer `which` (x itself where it has no convolution)."""
+        w = self.conv_weights[which]
+        if w is None:
+            return x
+        state = None
+        if self._conv_floats:
+            if cache.block_state is None:
+                raise ops.KernelError("sandwich_norm block: its input convolutions need the block's state slots (none were bound)")
+            first = self._conv_offset[which]
+            state = cache.block_state.view(cache.block_state.shape[0], -1)[:, first:first + self._conv_floats]
+        out = torch.empty(x.shape, device=x.device, dtype=self.dtype)
+        ops.causal_conv(x, w, None, state, step.state_slots, step.cu_seqlens_q, step.seq_index, step.num_seqs, out, add_input=True)
+        return out
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for p in self._parts:
@@ -231,6 +271,9 @@ class SandwichNormBlock(Block):
             self.mixer_scale = tensors[self.scale_names["mixer"]]
         if self.scale_names["ffn"] is not None:
             self.ffn_scale = tensors[self.scale_names["ffn"]]
+        for which, name in self.conv_names.items():
+            if name is not None:
+                self.conv_weights[which] = tensors[name]
         for norm in (self.mixer_out_norm, self.ffn_out_norm):
             if norm is not None and norm.params() is None:
                 raise ValueError("sandwich_norm block: the norm on a sublayer's output must be a plain RMS norm")
@@ -264,7 +307,9 @@ class SandwichNormBlock(Block):
             x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
             PreNormBlock._before(self.mixer_norm)
             self.mixer_norm.forward(hidden, None, x)
-        step.weight_after = (self.feed_forward.first_weight() if self.feed_forward is not None else None) or after_block
+        ffn_first = self.feed_forward.first_weight() if self.feed_forward is not None else None
+        step.weight_after = ffn_first if ffn_first is not None else after_block
+        x = self._input_conv("mixer", x, step, cache)
         PreNormBlock._before(self.mixer)
         branch = self.mixer.forward(x, step, cache)
         step.weight_after = after_block
@@ -274,6 +319,7 @@ class SandwichNormBlock(Block):
                 x = torch.empty(hidden.shape, device=hidden.device, dtype=self.dtype)
                 PreNormBlock._before(self.ffn_norm)
                 self.ffn_norm.forward(hidden, None, x)
+            x = self._input_conv("ffn", x, step, cache)
             PreNormBlock._before(self.feed_forward)
             branch = self.feed_forward.forward(x, step)
             out = self._close(branch, self.ffn_out_norm, self.ffn_scale, hidden, norm_after)

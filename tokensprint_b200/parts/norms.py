@@ -22,15 +22,18 @@ class RMSNorm(Norm):
     graph_safe = True
     reads_through_ops = True
 
-    def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str, offset: float = 0.0) -> None:
+    def __init__(self, ctx: BuildContext, *, dim: int, eps: float, weight: str, offset: float = 0.0, scalar: bool = False) -> None:
         self.dim, self.eps, self.weight_name, self.offset = int(dim), float(eps), weight, float(offset)
+        self.scalar = bool(scalar)
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> list[TensorSpec]:
-        return [TensorSpec(self.weight_name, (self.dim,), "vector")]
+        return [TensorSpec(self.weight_name, () if self.scalar else (self.dim,), "vector")]
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name]
+        if self.scalar:
+            self.weight = self.weight.reshape(1).expand(self.dim).contiguous()
         if self.offset:
             self.weight = (self.weight + self.offset).contiguous()
 

@@ -88,10 +88,17 @@ class RoutedExperts(FeedForward):
         chosen = the `top` largest logits
         weights: `score` "sigmoid": w_e = sigmoid(z_e) (or that / their sum with `renormalize`);
                  "softmax_chosen": the softmax over the chosen logits alone
+                 "softmax_all": scores s = softmax(z) over all experts; the `top` largest of
+                 s + c are chosen (`correction` names c, a number per expert that steers the choice
+                 only) and the weights are the chosen s themselves (divided by their sum with `renormalize`)
         f = sum over chosen e of expert_e(w_e x)   (`weight_on` "input"; "output": w_e expert_e(x))
             + shared(x) if a shared expert is named (any feed-forward spec)
         expert(x) = W_down act(W_gate x, W_up x), `activation` "capped_glu" (with `limit`, `alpha`)
-                    or "swiglu" (silu(gate) * up)
+                    or "swiglu" (silu(gate) * up); "gelu": experts without a gate matrix,
+                    W_down gelu(W_up x) with the exact (erf) gelu
+        `identity` = n: the router has n more outputs than there are experts; the last n stand for
+                    identity experts, which have no tensors and whose output is their input x itself
+                    (times the weight; `weight_on` "output" only)
 
     Routing, the sort of the (token, choice) pairs by expert and both expert products run on the
     device with grids that depend on the token count only, so a decode step is a fixed kernel
@@ -104,11 +111,11 @@ class RoutedExperts(FeedForward):
     def __init__(self, ctx: BuildContext, *, hidden_size: int, num_experts: int, top: int, intermediate_size: int,
                  router: str, expert_prefix: str, limit: float = 0.0, alpha: float = 1.702, renormalize: bool = False,
                  weight_on: str = "input", shared: Optional[PartSpec] = None, router_bias: Optional[str] = None,
-                 score: str = "sigmoid", activation: str = "capped_glu") -> None:
+                 score: str = "sigmoid", activation: str = "capped_glu", correction: Optional[str] = None, identity: int = 0) -> None:
         self.hidden_size, self.num_experts, self.top = int(hidden_size), int(num_experts), int(top)
         self.intermediate_size, self.limit, self.alpha = int(intermediate_size), float(limit), float(alpha)
         self.renormalize = bool(renormalize)
-        if not 0 < self.top <= self.num_experts:
+        if not 0 < self.top:
             raise ValueError(f"routed experts: top {top} of {num_experts} experts")
         if weight_on not in ("input", "output"):
             raise ValueError(f"routed experts: weight_on must be 'input' or 'output', got {weight_on!r}")
@@ -117,6 +124,16 @@ class RoutedExperts(FeedForward):
         if activation not in ops.MOE_ACTIVATIONS:
             raise ValueError(f"routed experts: activation must be one of {sorted(ops.MOE_ACTIVATIONS)}, got {activation!r}")
         self.weight_on, self.score, self.activation = weight_on, score, activation
+        self.identity = int(identity)
+        if self.identity < 0 or (self.identity and weight_on != "output"):
+            raise ValueError("routed experts: identity experts hand on their input times the weight (weight_on = 'output')")
+        if self.top > self.num_experts + self.identity:
+            raise ValueError(f"routed experts: top {top} of {num_experts} + {identity} router outputs")
+        if correction is not None and score != "softmax_all":
+            raise ValueError("routed experts: a correction of the choice comes with score = 'softmax_all'")
+        self.gated = activation != "gelu"
+        self.correction_name = correction
+        self.correction: Optional[torch.Tensor] = None
         self.router_name, self.router_bias_name, self.prefix = router, router_bias, expert_prefix
         self.router_bias: Optional[torch.Tensor] = None
         self.shared = build_part("feed_forward", shared, ctx) if shared is not None else None
@@ -134,12 +151,15 @@ class RoutedExperts(FeedForward):
 
     def tensor_specs(self) -> list[TensorSpec]:
         H, I = self.hidden_size, self.intermediate_size
-        specs = [TensorSpec(self.router_name, (self.num_experts, H), "vector")]  # the router stays float32
+        outputs = self.num_experts + self.identity
+        specs = [TensorSpec(self.router_name, (outputs, H), "vector")]  # the router stays float32
         if self.router_bias_name is not None:
-            specs.append(TensorSpec(self.router_bias_name, (self.num_experts,), "vector"))
+            specs.append(TensorSpec(self.router_bias_name, (outputs,), "vector"))
+        if self.correction_name is not None:
+            specs.append(TensorSpec(self.correction_name, (outputs,), "vector"))
         for e in range(self.num_experts):
             g, u, d = self._expert_names(e)
-            specs += [TensorSpec(g, (I, H)), TensorSpec(u, (I, H)), TensorSpec(d, (H, I))]
+            specs += ([TensorSpec(g, (I, H))] if self.gated else []) + [TensorSpec(u, (I, H)), TensorSpec(d, (H, I))]
         if self.shared is not None:
             specs += self.shared.tensor_specs()
         return specs
@@ -148,8 +168,10 @@ class RoutedExperts(FeedForward):
         self.router = tensors[self.router_name]
         if self.router_bias_name is not None:
             self.router_bias = tensors[self.router_bias_name]
+        if self.correction_name is not None:
+            self.correction = tensors[self.correction_name]
         names = [self._expert_names(e) for e in range(self.num_experts)]
-        self.gate = torch.stack([tensors[g] for g, _, _ in names]).contiguous()
+        self.gate = torch.stack([tensors[g] for g, _, _ in names]).contiguous() if self.gated else None
         self.up = torch.stack([tensors[u] for _, u, _ in names]).contiguous()
         self.down = torch.stack([tensors[d] for _, _, d in names]).contiguous()
         if self.shared is not None:
@@ -160,7 +182,7 @@ class RoutedExperts(FeedForward):
         rows = residual if residual is not None else x  # float32 rows where the block has them, else their rounding
         chosen = torch.empty((T, top), device=dev, dtype=torch.int32)
         weights = torch.empty((T, top), device=dev, dtype=torch.float32)
-        ops.router(rows, self.router, top, self.renormalize, chosen, weights, bias=self.router_bias, score=self.score)
+        ops.router(rows, self.router, top, self.renormalize, chosen, weights, bias=self.router_bias, score=self.score, correction=self.correction)
         # both products take the same plan: the tensor cores only if both inner widths suit them
         tensor_cores = ops.moe_on_tensor_cores(x.dtype, self.hidden_size, self.intermediate_size)
         plan = ops.moe_plan(chosen, self.num_experts, ops.moe_row_tile(tensor_cores, T * top, self.num_experts))
@@ -177,7 +199,10 @@ class RoutedExperts(FeedForward):
                 ops.flush_gemm_chain()
             shared = self.shared.forward(x, step)
         out = torch.empty((T, self.hidden_size), device=dev, dtype=x.dtype)
-        ops.moe_combine(pair_out, shared, out, top, None if on_input else weights.view(-1))
+        if self.identity:  # pairs that chose an identity expert have no place in the plan: the combine reads x for them
+            ops.moe_combine(pair_out, shared, out, top, weights.view(-1), ids=chosen, num_experts=self.num_experts, x=x)
+        else:
+            ops.moe_combine(pair_out, shared, out, top, None if on_input else weights.view(-1))
         return out
 
 

@@ -96,3 +96,20 @@ class Scale(Transform):
     def forward(self, x: torch.Tensor, step: Optional[StepContext]) -> torch.Tensor:
         ops.scale_rows(x, self.factor)
         return x
+
+
+@register_part("transform", "softcap")
+class SoftCap(Transform):
+    """x <- cap * tanh(x / cap) in float32: logits bent smoothly into (-cap, cap)."""
+
+    graph_safe = True
+    reads_through_ops = True
+
+    def __init__(self, ctx: BuildContext, *, cap: float) -> None:
+        self.cap = float(cap)
+        if not self.cap > 0:
+            raise ValueError("softcap: the cap must be positive")
+
+    def forward(self, x: torch.Tensor, step: Optional[StepContext]) -> torch.Tensor:
+        ops.softcap_rows(x, self.cap)
+        return x
