@@ -119,10 +119,13 @@ def window_attention(h: torch.Tensor, positions: Sequence[int], m: dict, w: Weig
     q = (h @ w[p + "q"].to(dt).T).view(T, H, d)
     k = (h @ w[p + "k"].to(dt).T).view(T, G, d)
     v = (h @ w[p + "v"].to(dt).T).view(T, G, e)
-    q = q * query_temperature(positions, float(m["q_temp"]["coef"]), int(m["q_temp"]["every"])).to(dt)[:, None, None]
+    if m.get("q_temp") is not None:
+        q = q * query_temperature(positions, float(m["q_temp"]["coef"]), int(m["q_temp"]["every"])).to(dt)[:, None, None]
     pos = torch.as_tensor(list(positions), dtype=torch.long)
     dist = pos[:, None] - pos[None, :]
-    visible = (dist >= 0) & (dist < int(m["mask"]["size"]))
+    visible = dist >= 0
+    if m.get("mask") is not None:  # a configuration without one: every earlier key
+        visible = visible & (dist < int(m["mask"]["size"]))
     far = dist.clamp(min=0).to(dt)
     r1, r2 = w[p + "r1"].to(dt), w[p + "r2"].to(dt)
     heads = []
