@@ -144,10 +144,10 @@ def test_delta_scan_many_sequences_side_by_side_against_each_alone(H, G, d, e):
     data = [_delta_inputs(H, G, d, e, max(n, 1), 100 + i) for i, n in enumerate(lengths)]
     a_log, dt_bias = data[0][2], data[0][3]
     state = torch.zeros((40, H * d * e), device="cuda")
-    state[5] = 7.0  # the empty lane's slot must stay as it is
+    slots = [(3 * i) % 40 for i in range(40)]  # 3 and 40 have no common factor: every slot once
+    state[slots[5]] = 7.0  # the empty lane's slot must stay as it is
     x = torch.cat([data[i][0][:n] for i, n in enumerate(lengths)])
     gates = torch.cat([data[i][1][:n] for i, n in enumerate(lengths)])
-    slots = [(3 * i) % 40 for i in range(40)]  # 3 and 40 have no common factor: every slot once
     got = _delta_run(x, gates, a_log, dt_bias, state, slots, lengths, H, G, d, e)
     at = 0
     for i, n in enumerate(lengths):

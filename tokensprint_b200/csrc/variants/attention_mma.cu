@@ -47,7 +47,7 @@ constexpr unsigned TMA_SPIN_LIMIT = 1u << 22;
 #endif
 constexpr int TSTAGES = TS_DECODE_TMA_STAGES;           // key blocks in flight per CTA on the copy-engine path
 
-// Builds with TS_ATT_SCORED=1 also know a sink score per query head and a tanh cap on the scores; the others
+// Builds with TS_ATT_SCORED=1 also know a sink score per query head, a tanh cap on the scores and a logarithmic distance penalty; the others
 // carry none of that code (their callers are refused both).
 #ifndef TS_ATT_SCORED
 #define TS_ATT_SCORED 0
@@ -78,6 +78,8 @@ struct AttnParams {
   const float* head_sinks;        // [nq] one sink score per query head (has_sink is then 1 and sink_raw unused), or null
   float inv_scale;                // 1 / scale (a head's sink score in raw units)
   float cap_raw, cap_inv;         // cap / scale and scale / cap: a raw score s becomes cap_raw * tanh(s * cap_inv); cap_raw 0: no cap
+  const float* dist_r1;           // [nq] with dist_r2: the scaled score of key j for a query at position i loses r1 * ln(1 + r2 * (i - j)); null: no penalty
+  const float* dist_r2;
 #endif
   int* flat_prefix;               // even-share kernel: [B + 1] key blocks of the sequences before each one, left for its combine kernel
 };
@@ -118,6 +120,26 @@ __device__ __forceinline__ float capped_score(const AttnParams& p, float s) {
 #else
   return s;
 #endif
+}
+__device__ __forceinline__ bool has_distance(const AttnParams& p) {
+#if TS_ATT_SCORED
+  return p.dist_r1 != nullptr;
+#else
+  return false;
+#endif
+}
+// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units.
+__device__ __forceinline__ void row_distance(const AttnParams& p, int hk, int G, int r, float& a, float& b) {
+#if TS_ATT_SCORED
+  a = p.dist_r1[hk * G + r % G] * p.inv_scale;
+  b = p.dist_r2[hk * G + r % G];
+#else
+  a = b = 0.f;
+#endif
+}
+// What key j costs a query at position pos, in raw units (keys behind the query are masked later: their distance counts as 0).
+__device__ __forceinline__ float distance_penalty(float a, float b, int pos, int j) {
+  return a * __logf(fmaf(b, (float)max(pos - j, 0), 1.f));
 }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
@@ -367,6 +389,12 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     const int r = r0 + warp_row0 + g + 8 * h;
     row_pos[h] = r < rows_total ? start_pos + r / G : -1;
     row_lo[h] = row_pos[h] >= 0 ? first_visible_key(p, row_pos[h]) : 0;
+  }
+  float dist_a[2] = {0.f, 0.f}, dist_b[2] = {0.f, 0.f};
+  if (has_distance(p)) {
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+      if (row_pos[h] >= 0) row_distance(p, hk, G, r0 + warp_row0 + g + 8 * h, dist_a[h], dist_b[h]);
   }
   // Smallest position and largest window start among this warp's rows that exist: key blocks
   // between them are seen in full by every such row.  (Rows that do not exist are never
@@ -620,6 +648,13 @@ __global__ void __launch_bounds__(NWARPS * 32) attention_mma_kernel(const AttnPa
     }
     float m_new[2] = {m_run[0], m_run[1]};
     const int wk0 = kbase + key0;  // first key this warp scores in this block
+    if (has_distance(p)) {
+#pragma unroll
+      for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          s[nt][e] -= distance_penalty(dist_a[e >> 1], dist_b[e >> 1], row_pos[e >> 1], wk0 + nt * 8 + tq * 2 + (e & 1));
+    }
     const bool unmasked = (wk0 + NTILES * 8 - 1 <= warp_min_pos) && (wk0 >= warp_max_lo);
     if (unmasked) {
 #pragma unroll
@@ -936,6 +971,14 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
       row_pos[mt][h] = r < rows_total ? start_pos + r / G : -1;
       row_lo[mt][h] = row_pos[mt][h] >= 0 ? first_visible_key(p, row_pos[mt][h]) : 0;
     }
+  float dist_a[PF_MT][2], dist_b[PF_MT][2];
+#pragma unroll
+  for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      dist_a[mt][h] = dist_b[mt][h] = 0.f;
+      if (has_distance(p) && row_pos[mt][h] >= 0) row_distance(p, hk, G, r0 + warp_row0 + mt * 16 + g + 8 * h, dist_a[mt][h], dist_b[mt][h]);
+    }
   // Positions of this warp's first and last row: blocks of keys between them need no mask.
   const int warp_first_pos = start_pos + min(r0 + warp_row0, rows_total - 1) / G;
   const int warp_rows_valid = (r0 + warp_row0 + 16 * PF_MT <= rows_total);
@@ -1024,6 +1067,15 @@ __global__ void __launch_bounds__(PF_WARPS * 32, 2) attention_prefill_kernel(con
         for (int nt = 0; nt < NTILES; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e) s[mt][nt][e] = capped_score(p, s[mt][nt][e]);
+    }
+    if (has_distance(p)) {
+#pragma unroll
+      for (int mt = 0; mt < PF_MT; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < NTILES; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            s[mt][nt][e] -= distance_penalty(dist_a[mt][e >> 1], dist_b[mt][e >> 1], row_pos[mt][e >> 1], kbase + nt * 8 + tq * 2 + (e & 1));
     }
 #pragma unroll
     for (int mt = 0; mt < PF_MT; ++mt) {
@@ -1834,15 +1886,18 @@ TS_EXPORT int ts_attention_mma_last_launches(void) { return ts_attention_last_la
 // `chunk` > 0: queries see only the keys of their own block of `chunk` positions; `has_sink`: exp(sink_score)
 // joins every softmax's denominator.  (The even-share decode kernel below knows neither.)
 // `softcap` > 0: the scaled score passes through softcap * tanh(score / softcap); `head_sinks` [nq]: a sink score per
-// query head (instead of `sink_score`).
+// query head (instead of `sink_score`); `dist_r1`, `dist_r2` [nq]: the scaled score of key j for the query at position i
+// loses r1 * ln(1 + r2 * (i - j)) (after the cap, before the mask).
 TS_EXPORT int ts_attention_paged_mma_scored(const void* q, const void* kcache, const void* vcache, void* out,
                                             float* scratch, const int* cu_q, const int* ctx_len,
                                             const int* block_table, const int* seq_index, int max_blocks,
                                             int page, int T, int B, int max_q, int nq, int nkv, float scale,
                                             int window, int chunk, int has_sink, float sink_score, float softcap, const float* head_sinks,
-                                            int splits, int keys_per_split, int* counters, void* stream_) {
+                                            int splits, int keys_per_split, int* counters, void* stream_, const float* dist_r1,
+                                            const float* dist_r2) {
   if (T <= 0 || B <= 0) return 0;
-  if (!SCORED && (head_sinks != nullptr || softcap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (!SCORED && (head_sinks != nullptr || softcap > 0.f || dist_r1 != nullptr)) return TS_ERR_BAD_ARGUMENT;
+  if ((dist_r1 == nullptr) != (dist_r2 == nullptr) || (dist_r1 != nullptr && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
   if (head_sinks != nullptr) has_sink = 1;
   if (chunk < 0 || ((has_sink || softcap > 0.f) && !(scale > 0.f)) || softcap < 0.f) return TS_ERR_BAD_ARGUMENT;
   if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || page <= 0 || max_blocks <= 0 || max_q <= 0 || splits < 1 ||
@@ -1872,7 +1927,9 @@ TS_EXPORT int ts_attention_paged_mma_scored(const void* q, const void* kcache, c
   p.sink_raw = has_sink ? sink_score / scale : 0.f;
 #if TS_ATT_SCORED
   p.head_sinks = head_sinks;
-  p.inv_scale = (has_sink || softcap > 0.f) ? 1.f / scale : 0.f;
+  p.inv_scale = (has_sink || softcap > 0.f || dist_r1 != nullptr) ? 1.f / scale : 0.f;
+  p.dist_r1 = dist_r1;
+  p.dist_r2 = dist_r2;
   p.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
   p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
 #endif
@@ -1919,7 +1976,7 @@ TS_EXPORT int ts_attention_paged_mma_masked(const void* q, const void* kcache, c
                                             int* counters, void* stream_) {
   return ts_attention_paged_mma_scored(q, kcache, vcache, out, scratch, cu_q, ctx_len, block_table, seq_index, max_blocks, page, T, B,
                                        max_q, nq, nkv, scale, window, chunk, has_sink, sink_score, 0.f, nullptr, splits, keys_per_split,
-                                       counters, stream_);
+                                       counters, stream_, nullptr, nullptr);
 }
 
 TS_EXPORT int ts_attention_paged_mma_fused(const void* q, const void* kcache, const void* vcache, void* out,

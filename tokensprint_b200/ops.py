@@ -1651,7 +1651,8 @@ def _attention_error_word() -> torch.Tensor:
 
 ATTENTION_MMA_MAX_HEAD_DIM = 256
 ATTENTION_MMA_MAX_SPLITS = 64
-ATTENTION_MMA_DISTANCE = False  # whether the tensor-core kernels know the logarithmic distance penalty
+# TS_ATTENTION_MMA_DISTANCE=0 (for measurements): layers with a distance penalty run the CUDA-core kernel in bfloat16 too
+ATTENTION_MMA_DISTANCE = _os.environ.get("TS_ATTENTION_MMA_DISTANCE", "1") != "0"
 _attention_mma: dict[int, tuple] = {}
 
 
@@ -1672,7 +1673,7 @@ def _attention_mma_fns(head_dim: int, scored: bool = False):
         lib = _build.load_variant("attention_mma", {"TS_HEAD_DIM": head_dim, "TS_ATT_SCORED": 1} if scored else {"TS_HEAD_DIM": head_dim})
         run = lib.ts_attention_paged_mma_scored
         run.argtypes = ([_c_void_p] * 9 + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p, _c_int, _c_int,
-                                                         _c_void_p, _c_void_p])
+                                                         _c_void_p, _c_void_p, _c_void_p, _c_void_p])
         run.restype = _c_int
         scratch = lib.ts_attention_mma_scratch_floats
         scratch.argtypes = [_c_ll, _c_int]
@@ -1819,11 +1820,15 @@ def attention_paged_mma(
     chunk > 0: a query sees only the keys of its own block of `chunk` positions (blocks count from
     position 0); sink: a score that joins every softmax's denominator without a value; head_sinks
     [nq] float32: one such score per query head; softcap > 0: the scaled score goes through
-    softcap * tanh(s / softcap).
+    softcap * tanh(s / softcap); distance = (r1, r2), [nq] float32 each: the scaled score of key j for the
+    query at position i loses r1 * ln(1 + r2 * (i - j)).
     """
     flush_gemm_chain()
-    if distance is not None and not ATTENTION_MMA_DISTANCE:
-        raise KernelError("attention_paged_mma: this build knows no distance penalty")
+    if distance is not None:
+        for name, t in zip(("distance r1", "distance r2"), distance):
+            _cuda_contig(name, t, torch.float32)
+            if t.numel() != num_heads:
+                raise KernelError(f"attention: {name} must have one entry per query head ({num_heads}), got {t.numel()}")
     scored = head_sinks is not None or softcap > 0.0 or distance is not None
     run, _ = _attention_mma_fns(head_dim, scored)
     if head_sinks is not None:
@@ -1862,7 +1867,7 @@ def attention_paged_mma(
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(), seq_index.data_ptr(),
         block_table.shape[1], page_size, T, num_seqs, max_seqlen_q, nq, nkv, float(scale), int(window), int(chunk),
         0 if sink is None else 1, 0.0 if sink is None else float(sink), float(softcap), _ptr(head_sinks), int(splits), int(keys_per_split),
-        counters, _stream()))
+        counters, _stream(), None if distance is None else distance[0].data_ptr(), None if distance is None else distance[1].data_ptr()))
     if splits > 1:
         global launch_count
         launch_count += (_attention_scored if scored else _attention_flat)[d].ts_attention_mma_last_launches() - 1  # the combine kernel, if one ran
