@@ -407,7 +407,7 @@ def run_probe(args) -> int:
     if args.designs:  # the other design's named model (four layers at width 2,048)
         from tokensprint_b200.config.registry import get_model_config
 
-        cfg = get_model_config({"dazilix": "dazilix-w2048", "pekunex": "pekunex-w2048"}.get(args.designs, "fegetar-w2048"))
+        cfg = get_model_config({"dazilix": "dazilix-w2048", "pekunex": "pekunex-w2048", "vasosun": "vasosun-w2048"}.get(args.designs, "fegetar-w2048"))
     else:
         d = get_preset_dict(MODEL_NAME)
         d["num_hidden_layers"] = args.layers or 4
@@ -742,10 +742,10 @@ def main() -> int:
                         "(the events cost host time: take the throughput from a run without this option)")
     p.add_argument("--workload", choices=sorted(WORKLOADS), default=None,
                    help="a serving loop through generate() instead of the decode benchmark (one JSON line)")
-    p.add_argument("--designs", nargs="?", const="fegetar", default=None, choices=["fegetar", "dazilix", "pekunex"],
+    p.add_argument("--designs", nargs="?", const="fegetar", default=None, choices=["fegetar", "dazilix", "pekunex", "vasosun"],
                    help="another design beside Qwen3 dense at equal size (a few layers of realistic widths, random weights): prompt and "
                         "decode throughput and the design's kernels against their rooflines (one JSON line); "
-                        "without a name: Fegetar; pekunex runs beside Dazilix, the closest design")
+                        "without a name: Fegetar; pekunex and vasosun run beside Dazilix, the closest design")
     p.add_argument("--probe", choices=["decode", "prefill"], default=None,
                    help="run a few steps inside cudaProfilerStart/Stop for ncu and exit (see profiles/); with --designs: of Fegetar's named model")
     args = p.parse_args()

@@ -76,7 +76,7 @@ def test_causal_conv_in_portions_and_batches(taps, mode, in_dtype, out_dtype):
         rows = torch.cat([seqs[k][done[k]:done[k] + step[k]] for k in names])
         cu, seq = _batch([step[k] for k in names])
         out = torch.empty(rows.shape, device="cuda", dtype=out_dtype)
-        ops.causal_conv(_dev(rows, in_dtype), _dev(w), None, view, _i32([slot_of[k] for k in names]), cu, seq, len(names), out,
+        ops.causal_conv(_dev(rows, in_dtype), _dev(w.t().contiguous()), None, view, _i32([slot_of[k] for k in names]), cu, seq, len(names), out,
                         activation="silu" if mode == "silu" else None, add_input=mode == "add_input")
         at = 0
         for k in names:

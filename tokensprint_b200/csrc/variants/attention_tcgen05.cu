@@ -53,7 +53,7 @@ constexpr int MAX_TABLE = 1024;                   // block-table entries kept in
 constexpr uint32_t TMEM_COLS = 256;               // S: 64 columns, O_blk: 128 columns
 constexpr uint32_t TMEM_S = 0, TMEM_O = 64;
 
-// Builds with TS_ATT_SCORED=1 also know a sink score per query head and a tanh cap on the scores; the others
+// Builds with TS_ATT_SCORED=1 also know a sink score per query head, a tanh cap on the scores and a logarithmic distance penalty; the others
 // carry none of that code (their callers are refused both).
 #ifndef TS_ATT_SCORED
 #define TS_ATT_SCORED 0
@@ -73,6 +73,8 @@ struct Params {
   const float* head_sinks;  // [nq] one sink score per query head (has_sink is then 1 and sink_raw unused), or null
   float inv_scale;          // 1 / scale (a head's sink score in raw units)
   float cap_raw, cap_inv;   // cap / scale and scale / cap: a raw score s becomes cap_raw * tanh(s * cap_inv); cap_raw 0: no cap
+  const float* dist_r1;     // [nq] with dist_r2: the scaled score of key j for a query at position i loses r1 * ln(1 + r2 * (i - j)); null: no penalty
+  const float* dist_r2;
 #endif
   float scale_log2;
   long long* probe;  // TS_ATT_PROBE builds: clock stamps of CTA 0's first softmax warp and of its MMA thread
@@ -203,6 +205,26 @@ __device__ __forceinline__ bool has_cap(const Params& p) {
 #else
   return false;
 #endif
+}
+__device__ __forceinline__ bool has_distance(const Params& p) {
+#if TS_ATT_SCORED
+  return p.dist_r1 != nullptr;
+#else
+  return false;
+#endif
+}
+// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units.
+__device__ __forceinline__ void row_distance(const Params& p, int hk, int G, int r, float& a, float& b) {
+#if TS_ATT_SCORED
+  a = p.dist_r1[hk * G + r % G] * p.inv_scale;
+  b = p.dist_r2[hk * G + r % G];
+#else
+  a = b = 0.f;
+#endif
+}
+// What key j costs a query at position pos, in raw units (keys behind the query are masked: their distance counts as 0).
+__device__ __forceinline__ float distance_penalty(float a, float b, int pos, int j) {
+  return a * __logf(fmaf(b, (float)max(pos - j, 0), 1.f));
 }
 // Scores bent through a tanh cap, still in raw units: tanh(x) = 1 - 2 / (exp(2x) + 1), exact at both ends
 // (exp overflows to inf: 1; underflows to 0: -1), absolute error of a few 1e-7 in between.
@@ -362,6 +384,8 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
   const int r = r0 + tid;
   const int row_pos = (tid < RT && r < rows_total) ? start_pos + r / G : -1;
   const int row_lo = row_pos >= 0 ? first_visible_key(p, row_pos) : 0;
+  float dist_a = 0.f, dist_b = 0.f;
+  if (has_distance(p) && row_pos >= 0) row_distance(p, hk, G, r, dist_a, dist_b);
   float o[D];
 #pragma unroll
   for (int i = 0; i < D; ++i) o[i] = 0.f;
@@ -392,6 +416,10 @@ __global__ void __launch_bounds__(128, 2) attention_tcgen05_kernel(const __grid_
     if (has_cap(p)) {
 #pragma unroll
       for (int j = 0; j < BN; ++j) s[j] = capped_score(p, s[j]);
+    }
+    if (has_distance(p)) {
+#pragma unroll
+      for (int j = 0; j < BN; ++j) s[j] -= distance_penalty(dist_a, dist_b, row_pos, kbase + j);
     }
 
     // every key of the block is seen by every row of the tile that belongs to a token (rows that belong
@@ -848,6 +876,8 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
     const int r = r0 + t * RT + row;
     const int row_pos = (row < RT && r < rows_total) ? start_pos + r / G : -1;
     const int row_lo = row_pos >= 0 ? first_visible_key(p, row_pos) : 0;
+    float dist_a = 0.f, dist_b = 0.f;
+    if (has_distance(p) && row_pos >= 0) row_distance(p, hk, G, r, dist_a, dist_b);
     const int tile_first_pos = start_pos + (r0 + t * RT) / G;
     const int tile_last_pos = start_pos + (min(r0 + t * RT + RT, rows_total) - 1) / G;  // of the tile's rows that belong to a token
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
@@ -876,12 +906,21 @@ __global__ void __launch_bounds__(608, 1) attention_tcgen05_pair_kernel(const __
         tmem_ld32(s_addr, v0);
         tmem_ld32(s_addr + 32, v1);
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (has_cap(p)) {
-          // the capped scores take the raw ones' place in tensor memory: the second walk reads them from there
+        if (has_cap(p) || has_distance(p)) {
+          // the capped (and distance-charged) scores take the raw ones' place in tensor memory: the second walk reads them from there
+          if (has_cap(p)) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) {
-            v0[i] = __float_as_uint(capped_score(p, __uint_as_float(v0[i])));
-            v1[i] = __float_as_uint(capped_score(p, __uint_as_float(v1[i])));
+            for (int i = 0; i < 32; ++i) {
+              v0[i] = __float_as_uint(capped_score(p, __uint_as_float(v0[i])));
+              v1[i] = __float_as_uint(capped_score(p, __uint_as_float(v1[i])));
+            }
+          }
+          if (has_distance(p)) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+              v0[i] = __float_as_uint(__uint_as_float(v0[i]) - distance_penalty(dist_a, dist_b, row_pos, kbase + i));
+              v1[i] = __float_as_uint(__uint_as_float(v1[i]) - distance_penalty(dist_a, dist_b, row_pos, kbase + 32 + i));
+            }
           }
           tmem_st32(s_addr, v0);
           tmem_st32(s_addr + 32, v1);
@@ -1114,14 +1153,17 @@ TS_EXPORT int ts_attention_tcgen05_supported(int nq, int nkv, int page) {
 // rows), 1 one tile per CTA, 2 two tiles per CTA.
 // `error`: one int the kernel sets to 1 if one of its waits gave up.
 // `softcap` > 0: the scaled score passes through softcap * tanh(score / softcap); `head_sinks` [nq]: a sink score per
-// query head (instead of `sink_score`).
+// query head (instead of `sink_score`); `dist_r1`, `dist_r2` [nq]: the scaled score of key j for the query at position i
+// loses r1 * ln(1 + r2 * (i - j)) (after the cap, before the mask).
 TS_EXPORT int ts_attention_prefill_tcgen05_scored(const void* q, const void* kcache, const void* vcache, void* out,
                                                   const int* cu_q, const int* ctx_len, const int* block_table,
                                                   int max_blocks, int page, long long total_slots, int T, int B, int max_q,
                                                   int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
-                                                  float softcap, const float* head_sinks, int mode, int* error, void* stream_) {
+                                                  float softcap, const float* head_sinks, int mode, int* error, void* stream_,
+                                                  const float* dist_r1, const float* dist_r2) {
   if (T <= 0 || B <= 0) return 0;
-  if (!SCORED && (head_sinks != nullptr || softcap > 0.f)) return TS_ERR_BAD_ARGUMENT;
+  if (!SCORED && (head_sinks != nullptr || softcap > 0.f || dist_r1 != nullptr)) return TS_ERR_BAD_ARGUMENT;
+  if ((dist_r1 == nullptr) != (dist_r2 == nullptr) || (dist_r1 != nullptr && !(scale > 0.f))) return TS_ERR_BAD_ARGUMENT;
   if (head_sinks != nullptr) has_sink = 1;
   if (chunk < 0 || ((has_sink || softcap > 0.f) && !(scale > 0.f)) || softcap < 0.f) return TS_ERR_BAD_ARGUMENT;
   if (!ts_attention_tcgen05_supported(nq, nkv, page) || max_blocks <= 0 || max_q <= 0 || error == nullptr)
@@ -1144,7 +1186,9 @@ TS_EXPORT int ts_attention_prefill_tcgen05_scored(const void* q, const void* kca
   p.sink_raw = has_sink ? sink_score / scale : 0.f;
 #if TS_ATT_SCORED
   p.head_sinks = head_sinks;
-  p.inv_scale = (has_sink || softcap > 0.f) ? 1.f / scale : 0.f;
+  p.inv_scale = (has_sink || softcap > 0.f || dist_r1 != nullptr) ? 1.f / scale : 0.f;
+  p.dist_r1 = dist_r1;
+  p.dist_r2 = dist_r2;
   p.cap_raw = softcap > 0.f ? softcap / scale : 0.f;
   p.cap_inv = softcap > 0.f ? scale / softcap : 0.f;
 #endif
@@ -1192,5 +1236,5 @@ TS_EXPORT int ts_attention_prefill_tcgen05(const void* q, const void* kcache, co
                                            int nq, int nkv, float scale, int window, int chunk, int has_sink, float sink_score,
                                            int mode, int* error, void* stream_) {
   return ts_attention_prefill_tcgen05_scored(q, kcache, vcache, out, cu_q, ctx_len, block_table, max_blocks, page, total_slots, T, B, max_q,
-                                             nq, nkv, scale, window, chunk, has_sink, sink_score, 0.f, nullptr, mode, error, stream_);
+                                             nq, nkv, scale, window, chunk, has_sink, sink_score, 0.f, nullptr, mode, error, stream_, nullptr, nullptr);
 }

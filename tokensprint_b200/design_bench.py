@@ -16,6 +16,14 @@ attention with a sink per head beside a matrix memory; a state-space layer; dens
 Dazilix, the closest design the engine has (attention with a sink and a linear recurrence), at equal
 width, depth, heads and feed-forward weight per token, with the distance of Pekunex's attention,
 recurrence and small kernels from their rooflines next to the like kernels of Dazilix.
+
+`python bench.py --designs vasosun` runs Vasosun (windowed attention with a query temperature and a
+distance penalty, latent attention with a query latent and a layer that reads its cached rows, the
+gated delta rule, routed experts without gates among which identity experts, every sublayer between
+two norms and behind a short convolution of its input) beside Dazilix, the closest design the engine
+has (the same block arrangement, attention and a linear recurrence, routed experts), at equal width,
+depth, heads and expert sizes, with the distance of Vasosun's attention, recurrence and small kernels
+from their rooflines next to the like kernels of Dazilix.
 """
 
 from __future__ import annotations
@@ -116,6 +124,86 @@ def pekunex_config(s: dict) -> dict:
 def dazilix_beside_pekunex(s: dict) -> dict:
     d = next(v for k, v in DAZILIX_SIZES.items() if v["width"] == s["width"])
     return dazilix_config(d)
+
+
+# Vasosun at the same widths: a windowed attention (heads of 128, a window that holds the prompt, so that it does the work
+# of Dazilix's attention), a latent attention (512 + 64 cached per token, queries through a latent of three quarters of the
+# width), a second one that reads the first one's rows, and a delta layer whose state is [heads, 64, 128] float32 per request
+# as Dazilix's recurrent layer's; routed experts of Dazilix's sizes (two more router outputs are identity experts).
+VASOSUN_SIZES = {
+    "w2048": dict(width=2048, heads=16, layers=4, experts=16, top=2, expert_ff=1024, identity=2, delta_dim=64, delta_vdim=128, window=4096,
+                  kv_rank=512, rot_dim=64, q_rank=1536, taps=4),
+    "w4096": dict(width=4096, heads=32, layers=4, experts=32, top=4, expert_ff=1536, identity=2, delta_dim=64, delta_vdim=128, window=4096,
+                  kv_rank=512, rot_dim=64, q_rank=3072, taps=4),
+}
+
+
+def vasosun_config(s: dict) -> dict:
+    att = {"heads": s["heads"], "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": s["window"]},
+           "q_temp": {"coef": 0.5, "every": 1024}}
+    lat = {"heads": s["heads"], "dim": 128, "rot_dim": s["rot_dim"], "vdim": 128, "kv_rank": s["kv_rank"], "q_rank": s["q_rank"],
+           "scale": 192 ** -0.5, "rot": {"base": 1000000.0, "dims": s["rot_dim"],
+                                         "scaling": {"factor": 4.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    delta = {"heads": s["heads"], "kv_heads": s["heads"], "dim": s["delta_dim"], "vdim": s["delta_vdim"], "conv": 4}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"]}}
+    return {"architecture": "Vasosun", "vocab": VOCAB, "width": s["width"], "norm": {"eps": 1e-6}, "canon": {"taps": s["taps"]},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}}, "logit_softcap": 30.0,
+            "layers": [{"type": "attention", "mixer": att, "mlp": moe}, {"type": "latent_attention", "mixer": lat, "mlp": moe},
+                       {"type": "latent_attention", "mixer": dict(lat, kv_from=1), "mlp": moe}, {"type": "delta", "mixer": delta, "mlp": moe}]}
+
+
+def dazilix_beside_vasosun(s: dict) -> dict:
+    d = next(v for k, v in DAZILIX_SIZES.items() if v["width"] == s["width"])
+    return dazilix_config(d)
+
+
+def _vasosun_rooflines(s: dict, m: dict, peaks: dict) -> dict[str, Any]:
+    """Vasosun's recurrence and small kernels against their rooflines, from the per-class timers.  The delta
+    rule: a prompt costs 8 float32 operations per state entry and token (decay, two read-outs of the decayed
+    state, the update) against the FFMA rate of the SMs at their top clock; a decode step reads and writes every
+    request's state once, against the measured copy bandwidth.  The convolutions (two per layer on the normed
+    rows, one on q, k, v of the delta layer), the kernels that close a sublayer, and the kernel between the
+    attention's projections and attention move their inputs and outputs once, against the same."""
+    out: dict[str, Any] = {}
+    H, d, e, W, L = s["heads"], s["delta_dim"], s["delta_vdim"], s["width"], s["layers"]
+    entries = H * d * e
+    ffma_peak = 148 * 128 * 2 * peaks.get("sm_max_mhz", 1965.0) * 1e6
+    hbm = peaks["hbm_gbs"] * 1e9
+    T = PREFILL_TOKENS
+    chans = 2 * H * d + H * e
+    small = {
+        "causal_conv": 2 * L * W * (2 + 2) + chans * (2 + 4),       # normed rows in and out in bf16, twice a layer; q, k, v in bf16, out float32
+        "branch_norm_add": 2 * L * W * 12,                           # the branch (bf16), the stream (float32, read and written), the next input (bf16)
+        "qkv_prepare": 2 * (H + 16) * 128 * 2,                       # one attention: q, k, v read and written
+        "gla_norm_gate": H * e * (4 + 2 + 2),                        # the read-out float32, gate and result bf16
+        "latent_prepare": 2 * (H * 192 * 2 + 576 * 2),               # two latent layers: queries read, rotated parts and the cached row written
+    }
+    for phase, kernels, tokens in [("prefill", m["prefill_kernels"], T)] + [(f"decode_b{b}", m[f"decode_b{b}_kernels"], b) for b in DECODE_BATCHES]:
+        ms = kernels.get("delta_scan", {}).get("ms", 0.0)
+        if ms > 0:
+            out[f"{phase}_delta_scan_ms"] = round(ms, 4)
+            if phase == "prefill":
+                out["prefill_delta_scan_of_ffma_peak"] = round(8.0 * T * entries / (ms * 1e-3) / ffma_peak, 3)
+            else:
+                out[f"{phase}_delta_scan_of_hbm_peak"] = round(tokens * entries * 8 / (ms * 1e-3) / hbm, 3)
+        for name, per_token in small.items():
+            ms = kernels.get(name, {}).get("ms", 0.0)
+            if ms > 0:
+                out[f"{phase}_{name}_ms"] = round(ms, 4)
+                if phase == "prefill":
+                    out[f"prefill_{name}_of_hbm_peak"] = round(tokens * per_token / (ms * 1e-3) / hbm, 3)
+    # the latent attention kernel, as Fegetar's is counted: per (query, key, head) 576 + 512 multiply-adds; a decode step reads every cached row once per layer
+    ms = m["prefill_kernels"].get("latent_attention_mma", {}).get("ms", 0.0)
+    pairs = T * (T + 1) / 2
+    if ms > 0:
+        out["prefill_latent_attention_ms"] = round(ms, 3)
+        out["prefill_latent_attention_of_bf16_peak"] = round(2 * 2 * H * pairs * (576 + 512) / (ms * 1e-3) / (peaks["bf16_tflops"] * 1e12), 3)
+    for batch in DECODE_BATCHES:
+        ms = m[f"decode_b{batch}_kernels"].get("latent_attention_mma", {}).get("ms", 0.0)
+        if ms > 0:
+            out[f"decode_b{batch}_latent_attention_ms"] = round(ms, 4)
+            out[f"decode_b{batch}_latent_attention_of_hbm_peak"] = round(2 * batch * DECODE_CONTEXT * 576 * 2 / (ms * 1e-3) / hbm, 3)
+    return out
 
 
 def _pekunex_rooflines(s: dict, m: dict, peaks: dict) -> dict[str, Any]:
@@ -256,6 +344,11 @@ def _attention_rooflines(design: str, s: dict, m: dict, peaks: dict) -> dict[str
         names = ("attention_prefill_tcgen05", "attention_paged_mma")
         flops = L * 4 * H * 128 * pairs
         row_bytes = 2 * 8 * 128 * 2
+    elif design == "vasosun":
+        L = 1  # the windowed attention (the latent layers have a kernel of their own)
+        names = ("attention_prefill_tcgen05", "attention_paged_mma", "attention_paged_simple")
+        flops = L * 4 * H * 128 * pairs
+        row_bytes = 2 * 8 * 128 * 2
     elif design == "dazilix":
         L = s["layers"] - len(DAZILIX_RECURRENT_LAYERS)
         names = ("attention_prefill_tcgen05", "attention_paged_mma")
@@ -328,10 +421,12 @@ def run(steps: int, warmup: int, peaks: dict, which: str = "fegetar") -> dict[st
 
     result: dict[str, Any] = {"metric": "design_comparison", "dtype": "bf16", "data": "synthetic, random weights",
                               "prefill_tokens": PREFILL_TOKENS, "decode_context": DECODE_CONTEXT, "sizes": {}}
-    sizes = {"dazilix": DAZILIX_SIZES, "pekunex": PEKUNEX_SIZES}.get(which, SIZES)
+    sizes = {"dazilix": DAZILIX_SIZES, "pekunex": PEKUNEX_SIZES, "vasosun": VASOSUN_SIZES}.get(which, SIZES)
     for name, s in sizes.items():
         row: dict[str, Any] = {"size": s}
-        if which == "pekunex":
+        if which == "vasosun":
+            pair = (("vasosun", vasosun_config(s)), ("dazilix", dazilix_beside_vasosun(s)))
+        elif which == "pekunex":
             pair = (("pekunex", pekunex_config(s)), ("dazilix", dazilix_beside_pekunex(s)))
         elif which == "dazilix":
             pair = (("dazilix", dazilix_config(s)), ("qwen3", qwen3_beside_dazilix(s)))
@@ -342,9 +437,11 @@ def run(steps: int, warmup: int, peaks: dict, which: str = "fegetar") -> dict[st
             model = random_model(cfg, seed=1, device="cuda", dtype="bfloat16", generate_on_device=True)
             m = _measure(model, steps, warmup)
             m["weight_bytes"] = model.weight_bytes()
-            sd = DAZILIX_SIZES[name] if (which == "pekunex" and design == "dazilix") else s
+            sd = DAZILIX_SIZES[name] if (which in ("pekunex", "vasosun") and design == "dazilix") else s
             m.update(_attention_rooflines(design, sd, m, peaks))
-            if which == "pekunex":
+            if which == "vasosun":
+                m.update(_vasosun_rooflines(s, m, peaks) if design == "vasosun" else _dazilix_rooflines(sd, m, peaks))
+            elif which == "pekunex":
                 m.update(_pekunex_rooflines(s, m, peaks) if design == "pekunex" else _dazilix_rooflines(sd, m, peaks))
             elif which == "dazilix":
                 m.update(_dazilix_rooflines(s, m, peaks) if design == "dazilix" else _qwen3_norm_roofline(s, m, peaks))

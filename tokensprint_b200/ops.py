@@ -1005,20 +1005,20 @@ def causal_conv(xin: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tens
                 cu_seqlens: torch.Tensor, seq_index: torch.Tensor, num_seqs: int, out: torch.Tensor, activation: Optional[str] = None,
                 add_input: bool = False) -> None:
     """A short causal convolution over time on every channel of xin [T, C] (a view of a wider matrix
-    is fine): out[t] = act(sum_j taps[:, j] * x[t - (K-1) + j] + bias), or with `add_input`
-    x[t] + that.  taps [C, K] float32 (the last column weighs the current token), bias [C] float32 or
-    None.  conv_state [slots, >= (K-1)*C] float32 (a view with a row stride is fine) holds the last
+    is fine): out[t] = act(sum_j taps[j] * x[t - (K-1) + j] + bias), or with `add_input`
+    x[t] + that.  taps [K, C] float32, tap by tap (the last row weighs the current token; a checkpoint's
+    [C, K] is transposed once at load), bias [C] float32 or None.  conv_state [slots, >= (K-1)*C] float32 (a view with a row stride is fine) holds the last
     K - 1 inputs of every request, oldest first; it is read for the inputs before a portion and then
     brought up to date with the portion's last inputs (K = 1: there is none, and conv_state may be None).
     Sums in float32; xin and out may differ in type."""
     flush_gemm_chain()
     T, C = xin.shape
-    K = taps.shape[1]
+    K = taps.shape[0]
     _matrix_view("causal_conv: xin", xin, T, C)
     _matrix_view("causal_conv: out", out, T, C)
     _cuda_contig("taps", taps, torch.float32)
-    if taps.shape != (C, K):
-        raise KernelError(f"causal_conv: taps must be [{C}, K], got {tuple(taps.shape)}")
+    if taps.shape != (K, C):
+        raise KernelError(f"causal_conv: taps must be [K, {C}], got {tuple(taps.shape)}")
     if bias is not None:
         _cuda_contig("bias", bias, torch.float32)
     if K > 1 and (conv_state is None or conv_state.dtype != torch.float32 or conv_state.dim() != 2 or conv_state.stride(1) != 1
@@ -1031,9 +1031,6 @@ def causal_conv(xin: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tens
         xin.data_ptr(), _act_code("xin", xin), xin.stride(0), taps.data_ptr(), _ptr(bias), K, state_ptr, state_stride,
         state_slots.data_ptr(), cu_seqlens.data_ptr(), seq_index.data_ptr(), out.data_ptr(), _act_code("out", out), out.stride(0), T, C,
         CONV_ACTIVATIONS[activation], 1 if add_input else 0, _stream()))
-    if K > 1:
-        _check("ssm_conv_state", _fn("ts_ssm_conv_state")(xin.data_ptr(), _act_code("xin", xin), xin.stride(0), K, state_ptr, state_stride,
-                                                          state_slots.data_ptr(), cu_seqlens.data_ptr(), int(num_seqs), C, _stream()))
 
 
 DELTA_MAX_KEY_DIM = 1024
@@ -2010,7 +2007,7 @@ def _attention_tcgen05_fns(scored: bool = False):
         lib = _build.load_variant("attention_tcgen05", {"TS_HEAD_DIM": ATTENTION_TCGEN05_HEAD_DIM})
         run = lib.ts_attention_prefill_tcgen05_scored
         run.argtypes = ([_c_void_p] * 7 + [_c_int, _c_int, _c_ll] + [_c_int] * 5 + [_c_float, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p,
-                                                                                     _c_int, _c_void_p, _c_void_p])
+                                                                                     _c_int, _c_void_p, _c_void_p, _c_void_p, _c_void_p])
         run.restype = _c_int
         ok = lib.ts_attention_tcgen05_supported
         ok.argtypes = [_c_int, _c_int, _c_int]
@@ -2050,6 +2047,7 @@ def attention_prefill_tcgen05(
     sink: Optional[float] = None,
     softcap: float = 0.0,
     head_sinks: Optional[torch.Tensor] = None,
+    distance: Optional[tuple[torch.Tensor, torch.Tensor]] = None,
 ) -> None:
     """Causal attention of prompt portions over the paged cache, tcgen05 tensor cores, head size 128.
 
@@ -2058,8 +2056,13 @@ def attention_prefill_tcgen05(
     their own, 0 chooses by the longest portion.
     """
     flush_gemm_chain()
-    run, ok = _attention_tcgen05_fns(head_sinks is not None or softcap > 0.0)
+    run, ok = _attention_tcgen05_fns(head_sinks is not None or softcap > 0.0 or distance is not None)
     d = ATTENTION_TCGEN05_HEAD_DIM
+    if distance is not None:
+        for name, t in zip(("distance r1", "distance r2"), distance):
+            _cuda_contig(name, t, torch.float32)
+            if t.numel() != num_heads:
+                raise KernelError(f"attention_prefill_tcgen05: {name} must have one entry per query head ({num_heads}), got {t.numel()}")
     for name, t in (("q", q), ("k_cache", k_cache), ("v_cache", v_cache), ("out", out)):
         _cuda_contig(name, t, torch.bfloat16)
     for name, t in (("cu_seqlens_q", cu_seqlens_q), ("context_lens", context_lens), ("block_table", block_table)):
@@ -2088,7 +2091,8 @@ def attention_prefill_tcgen05(
         cu_seqlens_q.data_ptr(), context_lens.data_ptr(), block_table.data_ptr(),
         block_table.shape[1], page_size, k_cache.shape[0] * page_size, T, num_seqs, max_seqlen_q, nq, nkv,
         float(scale), int(window), int(chunk), 0 if sink is None else 1, 0.0 if sink is None else float(sink), float(softcap),
-        _ptr(head_sinks), int(mode), error.data_ptr(), _stream()))
+        _ptr(head_sinks), int(mode), error.data_ptr(), _stream(), None if distance is None else distance[0].data_ptr(),
+        None if distance is None else distance[1].data_ptr()))
 
 
 # ---------------------------------------------------------------------------
@@ -2436,7 +2440,8 @@ _TIMED = ("embed_gather", "feed_tokens", "add_rmsnorm", "residual_add", "swiglu"
           "rmsnorm_add", "round_rows", "latent_prepare", "latent_attention_simple", "latent_attention_mma", "gelu_tanh", "capped_glu", "gelu_gate_rows",
           "router_topk", "router", "moe_plan", "moe_gate_up", "moe_down", "moe_combine", "branch_norm_add", "stream_add",
           "qk_joint_norm_rope_store", "gla_scan", "gla_norm_gate", "linear_scan", "rows_dot_f32", "mlstm_gate_scan", "mlstm_norm_gate",
-          "ssm_conv", "ssm_gate_norm", "scale_rows", "weighted_sum", "rope_table", "qkv_prepare", "gate_rows")
+          "ssm_conv", "ssm_gate_norm", "scale_rows", "weighted_sum", "rope_table", "qkv_prepare", "gate_rows", "causal_conv", "delta_scan",
+          "softcap_rows")
 _plain_functions: dict[str, object] = {}
 _kernel_events: list[tuple[str, "torch.cuda.Event", "torch.cuda.Event"]] = []
 

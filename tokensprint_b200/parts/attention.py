@@ -339,8 +339,7 @@ class AttentionMixer(Mixer):
                 # few rows per sequence: the decode kernels, keys spread over CTAs
                 self._attend_decode(q, out, step, cache, tables, 0, B, step.max_seqlen_q)
                 return
-            # (the tcgen05 kernel knows no distance penalty: such layers run the mma.sync prompt kernel)
-            prompts_on_tcgen05 = self.distance is None and ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
+            prompts_on_tcgen05 = ops.attention_tcgen05_supported(nq, nkv, d, step.page_size)
             if prompts_on_tcgen05 and few_rows and 0 < singles < B:
                 # Single decoded tokens beside portions of prompts (the runner put the single tokens'
                 # requests first): each kind to its own kernel.  Through the prompt kernel a decoded

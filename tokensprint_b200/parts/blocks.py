@@ -273,7 +273,7 @@ class SandwichNormBlock(Block):
             self.ffn_scale = tensors[self.scale_names["ffn"]]
         for which, name in self.conv_names.items():
             if name is not None:
-                self.conv_weights[which] = tensors[name]
+                self.conv_weights[which] = tensors[name].t().contiguous()  # tap by tap, as the kernel reads them
         for norm in (self.mixer_out_norm, self.ffn_out_norm):
             if norm is not None and norm.params() is None:
                 raise ValueError("sandwich_norm block: the norm on a sublayer's output must be a plain RMS norm")

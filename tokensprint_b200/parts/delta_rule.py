@@ -75,7 +75,8 @@ class GatedDeltaRule(Mixer):
         n = self.names
         self.in_weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]], tensors[n["gate"]]], dim=0).contiguous()
         self.gate_rows = torch.cat([tensors[n["beta"]], tensors[n["decay"]]], dim=0).contiguous()
-        self.conv_weight = torch.cat([tensors[n["q_conv"]], tensors[n["k_conv"]], tensors[n["v_conv"]]], dim=0).contiguous()
+        # the three convolutions as one, tap by tap [taps, channels], as the kernel reads them
+        self.conv_weight = torch.cat([tensors[n["q_conv"]], tensors[n["k_conv"]], tensors[n["v_conv"]]], dim=0).t().contiguous()
         self.a_log, self.dt_bias = tensors[n["a_log"]], tensors[n["dt_bias"]]
         self.norm_weight, self.o_weight = tensors[n["norm"]], tensors[n["o"]]
 
