@@ -137,8 +137,8 @@ def test_delta_scan_whole_in_portions_and_token_by_token(H, G, d, e):
 
 @pytest.mark.parametrize("H, G, d, e", [(6, 3, 20, 10), (2, 2, 64, 64)])
 def test_delta_scan_many_sequences_side_by_side_against_each_alone(H, G, d, e):
-    """Forty sequences of unequal length (one of them empty: a padded lane) in one launch: the thread shape
-    of the kernel follows the batch's size, the results do not, beyond rounding."""
+    """Forty sequences of unequal length (one of them empty: a padded lane) in one launch, their slots in
+    any order: each as it is alone."""
     lengths = [(7 * i) % 23 + (0 if i == 5 else 1) for i in range(40)]
     lengths[5] = 0
     data = [_delta_inputs(H, G, d, e, max(n, 1), 100 + i) for i, n in enumerate(lengths)]
