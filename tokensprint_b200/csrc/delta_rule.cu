@@ -154,25 +154,26 @@ __global__ void __launch_bounds__(DR_THREADS) delta_scan_kernel(
       for (int m = 0; m < M; ++m) {
         kv[m] = k4[r + R * m];
         const float4 qv = q4[r + R * m];
-        S[4 * m + 0] *= g, S[4 * m + 1] *= g, S[4 * m + 2] *= g, S[4 * m + 3] *= g;
         rk[0] = fmaf(S[4 * m + 0], kv[m].x, rk[0]), rq[0] = fmaf(S[4 * m + 0], qv.x, rq[0]);
         rk[1] = fmaf(S[4 * m + 1], kv[m].y, rk[1]), rq[1] = fmaf(S[4 * m + 1], qv.y, rq[1]);
         rk[0] = fmaf(S[4 * m + 2], kv[m].z, rk[0]), rq[0] = fmaf(S[4 * m + 2], qv.z, rq[0]);
         rk[1] = fmaf(S[4 * m + 3], kv[m].w, rk[1]), rq[1] = fmaf(S[4 * m + 3], qv.w, rq[1]);
       }
+      // the sums run over the state as it was; the decay is one factor on each of them (S^T k of the decayed state is g S^T k)
       float sk = rk[0] + rk[1], sq = rq[0] + rq[1];
 #pragma unroll
       for (int o = R >> 1; o > 0; o >>= 1) {
         sk += __shfl_xor_sync(0xffffffffu, sk, o);
         sq += __shfl_xor_sync(0xffffffffu, sq, o);
       }
+      sk *= g, sq *= g;
       const float u = bs[tt] * (vs[tt * COLS + cl] - sk);
 #pragma unroll
       for (int m = 0; m < M; ++m) {
-        S[4 * m + 0] = fmaf(kv[m].x, u, S[4 * m + 0]);
-        S[4 * m + 1] = fmaf(kv[m].y, u, S[4 * m + 1]);
-        S[4 * m + 2] = fmaf(kv[m].z, u, S[4 * m + 2]);
-        S[4 * m + 3] = fmaf(kv[m].w, u, S[4 * m + 3]);
+        S[4 * m + 0] = fmaf(g, S[4 * m + 0], kv[m].x * u);
+        S[4 * m + 1] = fmaf(g, S[4 * m + 1], kv[m].y * u);
+        S[4 * m + 2] = fmaf(g, S[4 * m + 2], kv[m].z * u);
+        S[4 * m + 3] = fmaf(g, S[4 * m + 3], kv[m].w * u);
       }
       if (live && r == 0) out[(size_t)(t0 + tt) * H * e + (size_t)h * e + col] = fmaf(u, kqs[tt], sq);
     }
@@ -201,27 +202,40 @@ static int dr_launch(const float* x, long long ld, int q_off, int k_off, int v_o
                    slot_stride, state_slots, cu_seqlens, out, H, G, d, e, q_scale, unit_eps);
 }
 
-// How the state of one head is cut over threads for key width d: a thread holds 16 key channels of its value column (fewer
-// where the key is narrower, 32 where 16 each would need more than a warp's lanes), and as many lanes share a column as that
-// takes.  The scan waits on its own chain of updates, token after token; a thread's sixteen multiply-adds run as two chains
-// and every doubling of the lanes adds a round of shuffles to each token, so the fewest lanes that keep the registers
-// moderate are the fastest (measured at 16 heads of 64 x 128, 2,048 tokens: 16 lanes of 4 channels and each round fetched
-// after the one before 1.40 ms, 4 lanes of 16 channels and the fetch ahead 0.66 ms).
+// How the state of one head is cut over threads for key width d: up to 16 lanes share a value column and hold 4 key
+// channels each (8 or 16 where the key is wider than 64 or 128 entries; 32 lanes beyond 256).  The scan waits on its own
+// chain of updates, token after token, so its time hardly depends on the cut (measured at 16 heads of 64 x 128, 2,048
+// tokens: 4 lanes of 16 channels 0.72 ms, 8 of 8 0.68, 16 of 4 0.64, 32 of which half hold nothing 0.95); what brought it
+// there from 1.40 ms were the rows fetched a round ahead, the staging pass over all of a round's tokens at once and lane
+// counts known at compile time.
 TS_EXPORT int ts_delta_scan(const float* x, long long ld, int q_off, int k_off, int v_off, const float* ba, long long ld_ba, const float* a_log,
                             const float* dt_bias, float* state, long long slot_stride, const int* state_slots, const int* cu_seqlens,
-                            float* out, int B, int H, int G, int d, int e, float q_scale, float unit_eps, void* stream) {
+                            float* out, int B, int H, int G, int d, int e, float q_scale, float unit_eps, int lanes, void* stream) {
   if (B <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || d <= 0 || e <= 0) return TS_ERR_BAD_ARGUMENT;
   if (d > DR_MAX_KEY_DIM || B > 65535 * 16 || H > 65535) return TS_ERR_UNSUPPORTED_SIZE;
   cudaStream_t s = (cudaStream_t)stream;
 #define DR_GO(MM, RR) \
   return dr_launch<MM, RR>(x, ld, q_off, k_off, v_off, ba, ld_ba, a_log, dt_bias, state, slot_stride, state_slots, cu_seqlens, out, B, H, G, d, e, q_scale, unit_eps, s)
+  if (lanes > 0) {  // a given number of lanes per column (a power of two up to 32), for measurements
+    const int fours = (d + 4 * lanes - 1) / (4 * lanes);
+#define DR_LANES(RR)                        \
+  if (lanes == RR) {                        \
+    if (fours <= 1) DR_GO(1, RR);           \
+    if (fours <= 2) DR_GO(2, RR);           \
+    if (fours <= 4) DR_GO(4, RR);           \
+    return TS_ERR_UNSUPPORTED_SIZE;         \
+  }
+    DR_LANES(1) DR_LANES(2) DR_LANES(4) DR_LANES(8) DR_LANES(16) DR_LANES(32)
+#undef DR_LANES
+    return TS_ERR_BAD_ARGUMENT;
+  }
   if (d <= 4) DR_GO(1, 1);
-  if (d <= 8) DR_GO(2, 1);
-  if (d <= 16) DR_GO(4, 1);
-  if (d <= 32) DR_GO(4, 2);
-  if (d <= 64) DR_GO(4, 4);
-  if (d <= 128) DR_GO(4, 8);
+  if (d <= 8) DR_GO(1, 2);
+  if (d <= 16) DR_GO(1, 4);
+  if (d <= 32) DR_GO(1, 8);
+  if (d <= 64) DR_GO(1, 16);
+  if (d <= 128) DR_GO(2, 16);
   if (d <= 256) DR_GO(4, 16);
   if (d <= 512) DR_GO(4, 32);
   DR_GO(8, 32);

@@ -797,7 +797,7 @@ _SIGNATURES.update({
     "ts_causal_conv": [_c_void_p, _c_int, _c_ll, _c_void_p, _c_void_p, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                        _c_int, _c_ll, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_delta_scan": [_c_void_p, _c_ll, _c_int, _c_int, _c_int, _c_void_p, _c_ll, _c_void_p, _c_void_p, _c_void_p, _c_ll, _c_void_p, _c_void_p,
-                      _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_void_p],
+                      _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void_p],
     "ts_gate_rows": [_c_void_p, _c_void_p, _c_ll, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p],
     "ts_weighted_sum": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_float, _c_float, _c_float, _c_float, _c_int, _c_void_p, _c_int, _c_ll,
                         _c_void_p],
@@ -1034,6 +1034,9 @@ def causal_conv(xin: torch.Tensor, taps: torch.Tensor, bias: Optional[torch.Tens
 
 
 DELTA_MAX_KEY_DIM = 1024
+# TS_DELTA_LANES (for measurements): lanes that share a value column of the delta rule's state (a power of two up to 32);
+# unset or 0: the kernel's own choice by the key width
+DELTA_LANES = int(_os.environ.get("TS_DELTA_LANES", "0"))
 
 
 def delta_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch.Tensor, a_log: torch.Tensor, dt_bias: torch.Tensor,
@@ -1066,7 +1069,7 @@ def delta_scan(x: torch.Tensor, q_off: int, k_off: int, v_off: int, gates: torch
     _check("delta_scan", _fn("ts_delta_scan")(
         x.data_ptr(), x.stride(0), int(q_off), int(k_off), int(v_off), gates.data_ptr(), gates.stride(0), a_log.data_ptr(), dt_bias.data_ptr(),
         state.data_ptr(), state.stride(0), state_slots.data_ptr(), cu_seqlens.data_ptr(), out.data_ptr(), int(num_seqs), H, G, d, e,
-        float(q_scale), float(unit_eps), _stream()))
+        float(q_scale), float(unit_eps), DELTA_LANES, _stream()))
 
 
 WEIGHTED_SUM_MAX_INPUTS = 4
