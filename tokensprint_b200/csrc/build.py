@@ -236,7 +236,7 @@ def build_all() -> list[Path]:
     with ThreadPoolExecutor(max_workers=min(os.cpu_count() or 2, 8)) as pool:
         paths += list(pool.map(lambda d: build_variant("attention_mma", {"TS_HEAD_DIM": d}), ATTENTION_HEAD_DIMS))
     paths.append(build_variant("attention_tcgen05", {"TS_HEAD_DIM": 128}))
-    # the builds that also know a sink score per head and a cap on the scores, at the common head sizes (others at first use)
+    # the builds that also know a sink score per head, a cap on the scores and a distance penalty, at the common head sizes (others at first use)
     paths += [build_variant("attention_mma", {"TS_HEAD_DIM": d, "TS_ATT_SCORED": 1}) for d in (64, 128)]
     paths.append(build_variant("attention_tcgen05", {"TS_HEAD_DIM": 128, "TS_ATT_SCORED": 1}))
     paths.append(build_variant("latent_attention_mma", {"TS_LAT_RANK": 512, "TS_LAT_ROT": 64}))
