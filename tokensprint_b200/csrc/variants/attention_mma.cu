@@ -128,10 +128,11 @@ __device__ __forceinline__ bool has_distance(const AttnParams& p) {
   return false;
 #endif
 }
-// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units.
+// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units
+// and times ln 2 (the penalty is then one hardware logarithm to base 2 and one multiply).
 __device__ __forceinline__ void row_distance(const AttnParams& p, int hk, int G, int r, float& a, float& b) {
 #if TS_ATT_SCORED
-  a = p.dist_r1[hk * G + r % G] * p.inv_scale;
+  a = p.dist_r1[hk * G + r % G] * p.inv_scale * 0.69314718055994531f;
   b = p.dist_r2[hk * G + r % G];
 #else
   a = b = 0.f;
@@ -139,7 +140,7 @@ __device__ __forceinline__ void row_distance(const AttnParams& p, int hk, int G,
 }
 // What key j costs a query at position pos, in raw units (keys behind the query are masked later: their distance counts as 0).
 __device__ __forceinline__ float distance_penalty(float a, float b, int pos, int j) {
-  return a * __logf(fmaf(b, (float)max(pos - j, 0), 1.f));
+  return a * __log2f(fmaf(b, (float)max(pos - j, 0), 1.f));
 }
 __device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));

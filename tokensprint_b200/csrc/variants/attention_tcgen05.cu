@@ -213,10 +213,11 @@ __device__ __forceinline__ bool has_distance(const Params& p) {
   return false;
 #endif
 }
-// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units.
+// The two numbers of the distance penalty for row `r` of a (sequence, KV head) pair's rows, the first in raw score units
+// and times ln 2 (the penalty is then one hardware logarithm to base 2 and one multiply).
 __device__ __forceinline__ void row_distance(const Params& p, int hk, int G, int r, float& a, float& b) {
 #if TS_ATT_SCORED
-  a = p.dist_r1[hk * G + r % G] * p.inv_scale;
+  a = p.dist_r1[hk * G + r % G] * p.inv_scale * 0.69314718055994531f;
   b = p.dist_r2[hk * G + r % G];
 #else
   a = b = 0.f;
@@ -224,7 +225,7 @@ __device__ __forceinline__ void row_distance(const Params& p, int hk, int G, int
 }
 // What key j costs a query at position pos, in raw units (keys behind the query are masked: their distance counts as 0).
 __device__ __forceinline__ float distance_penalty(float a, float b, int pos, int j) {
-  return a * __logf(fmaf(b, (float)max(pos - j, 0), 1.f));
+  return a * __log2f(fmaf(b, (float)max(pos - j, 0), 1.f));
 }
 // Scores bent through a tanh cap, still in raw units: tanh(x) = 1 - 2 / (exp(2x) + 1), exact at both ends
 // (exp overflows to inf: 1; underflows to 0: -1), absolute error of a few 1e-7 in between.
