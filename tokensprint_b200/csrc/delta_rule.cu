@@ -202,12 +202,15 @@ static int dr_launch(const float* x, long long ld, int q_off, int k_off, int v_o
                    slot_stride, state_slots, cu_seqlens, out, H, G, d, e, q_scale, unit_eps);
 }
 
-// How the state of one head is cut over threads for key width d: up to 16 lanes share a value column and hold 4 key
-// channels each (8 or 16 where the key is wider than 64 or 128 entries; 32 lanes beyond 256).  The scan waits on its own
-// chain of updates, token after token, so its time hardly depends on the cut (measured at 16 heads of 64 x 128, 2,048
-// tokens: 4 lanes of 16 channels 0.72 ms, 8 of 8 0.68, 16 of 4 0.64, 32 of which half hold nothing 0.95); what brought it
-// there from 1.40 ms were the rows fetched a round ahead, the staging pass over all of a round's tokens at once and lane
-// counts known at compile time.
+// How the state of one head is cut over threads for key width d: a thread holds 16 key channels of its value column
+// (fewer where the key is narrower, 32 where 16 each would need more than a warp's lanes), and as many lanes share a
+// column as that takes.  The scan waits on its own chain of updates, token after token, so a prompt's time hardly depends
+// on the cut (measured at 16 heads of 64 x 128, 2,048 tokens: 4 lanes of 16 channels 0.66 to 0.72 ms, 8 of 8 0.68, 16 of 4
+// 0.62 to 0.64, 32 of which half hold nothing 0.95); what brought it there from 1.40 ms were the rows fetched a round
+// ahead, the staging pass over all of a round's tokens at once and lane counts known at compile time.  More lanes mean
+// more and smaller CTAs, which costs where many run side by side: with 16 lanes of 4 channels 32 heads took 0.81 ms
+// instead of 0.66, and a decode step of 64 sequences, which only reads and writes the states, 0.11 to 0.12 of the copy
+// bandwidth instead of 0.17 to 0.26.
 TS_EXPORT int ts_delta_scan(const float* x, long long ld, int q_off, int k_off, int v_off, const float* ba, long long ld_ba, const float* a_log,
                             const float* dt_bias, float* state, long long slot_stride, const int* state_slots, const int* cu_seqlens,
                             float* out, int B, int H, int G, int d, int e, float q_scale, float unit_eps, int lanes, void* stream) {
@@ -231,11 +234,11 @@ TS_EXPORT int ts_delta_scan(const float* x, long long ld, int q_off, int k_off, 
     return TS_ERR_BAD_ARGUMENT;
   }
   if (d <= 4) DR_GO(1, 1);
-  if (d <= 8) DR_GO(1, 2);
-  if (d <= 16) DR_GO(1, 4);
-  if (d <= 32) DR_GO(1, 8);
-  if (d <= 64) DR_GO(1, 16);
-  if (d <= 128) DR_GO(2, 16);
+  if (d <= 8) DR_GO(2, 1);
+  if (d <= 16) DR_GO(4, 1);
+  if (d <= 32) DR_GO(4, 2);
+  if (d <= 64) DR_GO(4, 4);
+  if (d <= 128) DR_GO(4, 8);
   if (d <= 256) DR_GO(4, 16);
   if (d <= 512) DR_GO(4, 32);
   DR_GO(8, 32);
